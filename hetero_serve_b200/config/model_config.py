@@ -95,6 +95,12 @@ def architecture_of(raw: Mapping[str, Any]) -> Architecture:
         if not isinstance(archs, (list, tuple)) or not isinstance(archs[0], str):
             raise ConfigError(f"'architectures' must be a list of names, got {archs!r}")
         return get_architecture(archs[0])
+    one = raw.get("architecture")            # some families name themselves with one string
+    if isinstance(one, str) and one in _ARCHITECTURES:
+        return _ARCHITECTURES[one]
+    if one is not None:
+        raise ConfigError(f"unknown architecture {one!r}; registered: "
+                          f"{registered_architectures()}")
     mt = raw.get("model_type")
     if mt in _MODEL_TYPES:
         return _ARCHITECTURES[_MODEL_TYPES[mt]]

@@ -12,7 +12,7 @@ __global__ void embed_kernel(float* __restrict__ x, const int* __restrict__ ids,
                              const int* __restrict__ pos, const int* __restrict__ req,
                              const T* __restrict__ wte, const T* __restrict__ wpe, int width,
                              int vocab, int n_pos, const int* __restrict__ feedback,
-                             int n_feedback, int* status) {
+                             int n_feedback, float scale, int* status) {
   pdl_trigger();
   const int t = blockIdx.x;
   float* row = x + (size_t)t * width;
@@ -37,9 +37,10 @@ __global__ void embed_kernel(float* __restrict__ x, const int* __restrict__ ids,
   const T* a = wte + (size_t)id * width;
   if (wpe != nullptr) {
     const T* b = wpe + (size_t)p * width;
-    for (int e = threadIdx.x; e < width; e += blockDim.x) row[e] = to_f(a[e]) + to_f(b[e]);
+    for (int e = threadIdx.x; e < width; e += blockDim.x)
+      row[e] = to_f(a[e]) * scale + to_f(b[e]);
   } else {
-    for (int e = threadIdx.x; e < width; e += blockDim.x) row[e] = to_f(a[e]);
+    for (int e = threadIdx.x; e < width; e += blockDim.x) row[e] = to_f(a[e]) * scale;
   }
 }
 
@@ -163,11 +164,12 @@ layernorm_warp_kernel(TO* __restrict__ out, const float* __restrict__ x,
 
 // feedback (may be null): `n_feedback` token ids kept on the device; a negative id -(s + 1) in
 // `ids` stands for feedback[s], so that a step can start before the host has seen the token the
-// previous step sampled.
+// previous step sampled.  `scale` multiplies the token row (1 for a table used as it is; the
+// product with 1 is exact).
 HS_EXPORT int hs_embed(float* x, const int* ids, const int* pos, const int* req, const void* wte,
                        const void* wpe, int n_tokens, int width, int vocab, int n_pos,
-                       int table_dtype, const int* feedback, int n_feedback, int* status,
-                       void* stream) {
+                       int table_dtype, const int* feedback, int n_feedback, float scale,
+                       int* status, void* stream) {
   if (!x || !ids || !pos || !req || !wte || !status) return HS_ERR_ARGUMENT;
   if (n_tokens <= 0) return HS_OK;
   cudaStream_t st = (cudaStream_t)stream;
@@ -175,11 +177,11 @@ HS_EXPORT int hs_embed(float* x, const int* ids, const int* pos, const int* req,
   if (table_dtype == HS_DT_F32)
     hs::embed_kernel<float><<<n_tokens, threads, 0, st>>>(
         x, ids, pos, req, (const float*)wte, (const float*)wpe, width, vocab, n_pos, feedback,
-        n_feedback, status);
+        n_feedback, scale, status);
   else if (table_dtype == HS_DT_BF16)
     hs::embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, st>>>(
         x, ids, pos, req, (const __nv_bfloat16*)wte, (const __nv_bfloat16*)wpe, width, vocab,
-        n_pos, feedback, n_feedback, status);
+        n_pos, feedback, n_feedback, scale, status);
   else
     return HS_ERR_UNSUPPORTED;
   HS_LAUNCH_CHECK();

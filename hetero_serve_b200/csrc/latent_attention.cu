@@ -1,0 +1,225 @@
+// Attention over a shared latent: per token the cache holds ONE row [latent (R) | rotated key
+// part (P)] for all heads.  Queries arrive absorbed: qa[h] = W_uk[h]^T q_plain[h] (R numbers)
+// and the rotated part qr[h] (P numbers), so that
+//
+//   score(i, j) = (qa_i . c_j + qr_i . kr_j) * scale        for every j <= i (causal)
+//   weights     = exp(score - m) / (sum_j exp(score_j - m) + exp(sink_h - m))
+//   out_lat[h]  = sum_j weight_j * c_j                        (R numbers; W_uv[h] follows)
+//
+// The sink of a head is a learned logit without key or value: it only enters the denominator.
+// Scores, the running maximum, the denominator and the accumulator are float32.
+//
+// Pool rows: [pages, page_size, R + P] in the cache type; row of position p of request r is
+// table[r, p / page_size] * page_size + p % page_size.
+#include "common.cuh"
+
+namespace hs {
+
+// -- append: RMS-norm the latent, copy the (already rotated) key part, write the cache row ------
+template <typename TC>
+__global__ void latent_append_kernel(TC* __restrict__ pool, const float* __restrict__ proj,
+                                     const float* __restrict__ norm_w,
+                                     const int* __restrict__ table,
+                                     const int* __restrict__ tok_pos,
+                                     const int* __restrict__ tok_req, int proj_stride, int c_off,
+                                     int R, int P, float eps, int page_size, int num_pages,
+                                     int max_pages, int* status) {
+  __shared__ float red[4];
+  __shared__ float bcast;
+  const int t = blockIdx.x;
+  const int r = tok_req[t];
+  if (r < 0) return;
+  const int p = tok_pos[t];
+  const int pi = p / page_size;
+  const int page = (p >= 0 && pi < max_pages) ? table[(size_t)r * max_pages + pi] : -1;
+  if (page < 0 || page >= num_pages) {
+    if (threadIdx.x == 0) atomicOr(status, HS_STATUS_BAD_PAGE);
+    return;
+  }
+  const float* src = proj + (size_t)t * proj_stride + c_off;
+  float ss = 0.f;
+  for (int e = threadIdx.x; e < R; e += blockDim.x) ss = fmaf(src[e], src[e], ss);
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float tot = 0.f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += red[i];
+    bcast = 1.0f / sqrtf(tot / (float)R + eps);
+  }
+  __syncthreads();
+  const float rs = bcast;
+  TC* dst = pool + ((size_t)page * page_size + (p % page_size)) * (R + P);
+  for (int e = threadIdx.x; e < R; e += blockDim.x) dst[e] = from_f<TC>(src[e] * rs * norm_w[e]);
+  for (int e = threadIdx.x; e < P; e += blockDim.x) dst[R + e] = from_f<TC>(src[R + e]);
+}
+
+// -- attention ---------------------------------------------------------------------------------
+constexpr int LA_TILE = 32;     // keys per tile: one per lane when scores are formed
+constexpr int LA_HB = 8;        // heads (warps) per block
+
+template <typename TC, int RC>
+__global__ void __launch_bounds__(LA_HB * 32)
+latent_attention_kernel(float* __restrict__ out, const float* __restrict__ qa,
+                        const float* __restrict__ qr, const TC* __restrict__ pool,
+                        const int* __restrict__ table, const int* __restrict__ tok_pos,
+                        const int* __restrict__ tok_req, const float* __restrict__ sink,
+                        int n_heads, int R, int P, int qr_stride, int qr_hstride, int qr_off,
+                        float scale, int page_size, int num_pages, int max_pages, int* status) {
+  extern __shared__ float smem[];
+  const int W = R + P;
+  const int ks = W | 1;                         // odd row stride: lanes on rows hit distinct banks
+  float* s_q = smem;                            // [LA_HB][W]
+  float* s_k = smem + LA_HB * W;                // [LA_TILE][ks]
+  const int t = blockIdx.x;
+  const int r = tok_req[t];
+  if (r < 0) return;
+  const int pos = tok_pos[t];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y * LA_HB + warp;
+  const bool live = h < n_heads;
+  // queries of this block's heads
+  for (int i = threadIdx.x; i < LA_HB * W; i += blockDim.x) {
+    const int hh = i / W, d = i - hh * W;
+    const int head = blockIdx.y * LA_HB + hh;
+    float v = 0.f;
+    if (head < n_heads)
+      v = d < R ? qa[((size_t)t * n_heads + head) * R + d]
+                : qr[(size_t)t * qr_stride + (size_t)head * qr_hstride + qr_off + (d - R)];
+    s_q[i] = v;
+  }
+  float m = live ? sink[h] : 0.f;               // the sink opens the running softmax: weight 1
+  float l = 1.f;
+  float acc[RC];
+#pragma unroll
+  for (int i = 0; i < RC; ++i) acc[i] = 0.f;
+  const float* q = s_q + warp * W;
+  for (int base = 0; base <= pos; base += LA_TILE) {
+    __syncthreads();                            // the tile before has been used (and s_q is set)
+    const int nk = min(LA_TILE, pos + 1 - base);
+    for (int j = warp; j < nk; j += LA_HB) {
+      const int kp = base + j;
+      const int pi = kp / page_size;
+      const int page = pi < max_pages ? table[(size_t)r * max_pages + pi] : -1;
+      float* dst = s_k + j * ks;
+      if (page < 0 || page >= num_pages) {
+        if (lane == 0) atomicOr(status, HS_STATUS_BAD_PAGE);
+        for (int d = lane; d < W; d += 32) dst[d] = 0.f;
+      } else {
+        const TC* src = pool + ((size_t)page * page_size + (kp % page_size)) * W;
+        for (int d = lane; d < W; d += 32) dst[d] = to_f(src[d]);
+      }
+    }
+    __syncthreads();
+    if (!live) continue;
+    float s = -INFINITY;
+    if (lane < nk) {
+      const float* kr = s_k + lane * ks;
+      float dot = 0.f;
+      for (int d = 0; d < W; ++d) dot = fmaf(q[d], kr[d], dot);
+      s = dot * scale;
+    }
+    const float m_new = fmaxf(m, warp_max(s));
+    const float corr = expf(m - m_new);
+    const float pj = lane < nk ? expf(s - m_new) : 0.f;
+    l = l * corr + warp_sum(pj);
+    m = m_new;
+#pragma unroll
+    for (int i = 0; i < RC; ++i) acc[i] *= corr;
+    for (int j = 0; j < nk; ++j) {
+      const float w = __shfl_sync(0xffffffffu, pj, j);
+      const float* kr = s_k + j * ks;
+#pragma unroll
+      for (int i = 0; i < RC; ++i) {
+        const int d = lane + 32 * i;
+        if (d < R) acc[i] = fmaf(w, kr[d], acc[i]);
+      }
+    }
+  }
+  if (!live) return;
+  const float inv = 1.0f / l;
+  float* o = out + ((size_t)t * n_heads + h) * R;
+#pragma unroll
+  for (int i = 0; i < RC; ++i) {
+    const int d = lane + 32 * i;
+    if (d < R) o[d] = acc[i] * inv;
+  }
+}
+
+}  // namespace hs
+
+HS_EXPORT int hs_latent_append(void* pool, const float* proj, const float* norm_w,
+                               const int* table, const int* tok_pos, const int* tok_req,
+                               int n_tokens, int proj_stride, int c_off, int R, int P, float eps,
+                               int page_size, int num_pages, int max_pages, int cache_dtype,
+                               int* status, void* stream) {
+  if (!pool || !proj || !norm_w || !table || !tok_pos || !tok_req || !status)
+    return HS_ERR_ARGUMENT;
+  if (R <= 0 || P < 0 || page_size <= 0) return HS_ERR_UNSUPPORTED;
+  if (n_tokens <= 0) return HS_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (cache_dtype == HS_DT_F32)
+    hs::latent_append_kernel<float><<<n_tokens, 128, 0, st>>>(
+        (float*)pool, proj, norm_w, table, tok_pos, tok_req, proj_stride, c_off, R, P, eps,
+        page_size, num_pages, max_pages, status);
+  else if (cache_dtype == HS_DT_BF16)
+    hs::latent_append_kernel<__nv_bfloat16><<<n_tokens, 128, 0, st>>>(
+        (__nv_bfloat16*)pool, proj, norm_w, table, tok_pos, tok_req, proj_stride, c_off, R, P,
+        eps, page_size, num_pages, max_pages, status);
+  else
+    return HS_ERR_UNSUPPORTED;
+  HS_LAUNCH_CHECK();
+  return HS_OK;
+}
+
+template <typename TC, int RC>
+static int launch_latent_attention(float* out, const float* qa, const float* qr, const void* pool,
+                                   const int* table, const int* tok_pos, const int* tok_req,
+                                   const float* sink, int n_tokens, int n_heads, int R, int P,
+                                   int qr_stride, int qr_hstride, int qr_off, float scale,
+                                   int page_size, int num_pages, int max_pages, int* status,
+                                   cudaStream_t st) {
+  const int W = R + P;
+  const size_t smem = ((size_t)hs::LA_HB * W + (size_t)hs::LA_TILE * (W | 1)) * sizeof(float);
+  if (smem > 200 * 1024) return HS_ERR_UNSUPPORTED;
+  auto kern = hs::latent_attention_kernel<TC, RC>;
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  dim3 grid(n_tokens, (n_heads + hs::LA_HB - 1) / hs::LA_HB);
+  kern<<<grid, hs::LA_HB * 32, smem, st>>>(out, qa, qr, (const TC*)pool, table, tok_pos, tok_req,
+                                           sink, n_heads, R, P, qr_stride, qr_hstride, qr_off,
+                                           scale, page_size, num_pages, max_pages, status);
+  HS_LAUNCH_CHECK();
+  return HS_OK;
+}
+
+HS_EXPORT int hs_latent_attention(float* out, const float* qa, const float* qr, const void* pool,
+                                  const int* table, const int* tok_pos, const int* tok_req,
+                                  const float* sink, int n_tokens, int n_heads, int R, int P,
+                                  int qr_stride, int qr_hstride, int qr_off, float scale,
+                                  int page_size, int num_pages, int max_pages, int cache_dtype,
+                                  int* status, void* stream) {
+  if (!out || !qa || !qr || !pool || !table || !tok_pos || !tok_req || !sink || !status)
+    return HS_ERR_ARGUMENT;
+  if (R <= 0 || R > 512 || P < 0 || n_heads <= 0 || page_size <= 0) return HS_ERR_UNSUPPORTED;
+  if (n_tokens <= 0) return HS_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int rc = (R + 31) / 32;
+#define HS_LA(TC, RC)                                                                         \
+  return launch_latent_attention<TC, RC>(out, qa, qr, pool, table, tok_pos, tok_req, sink,    \
+                                         n_tokens, n_heads, R, P, qr_stride, qr_hstride,      \
+                                         qr_off, scale, page_size, num_pages, max_pages,      \
+                                         status, st)
+#define HS_LA_RC(TC)                   \
+  do {                                 \
+    if (rc <= 2) HS_LA(TC, 2);         \
+    if (rc <= 4) HS_LA(TC, 4);         \
+    if (rc <= 8) HS_LA(TC, 8);         \
+    HS_LA(TC, 16);                     \
+  } while (0)
+  if (cache_dtype == HS_DT_F32) HS_LA_RC(float);
+  if (cache_dtype == HS_DT_BF16) HS_LA_RC(__nv_bfloat16);
+#undef HS_LA_RC
+#undef HS_LA
+  return HS_ERR_UNSUPPORTED;
+}

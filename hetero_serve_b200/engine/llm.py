@@ -40,7 +40,8 @@ class LLMEngine:
             max_requests=cfg.live_requests, dtype=TORCH_DTYPES[cfg.dtype], device=cfg.device,
             ops=ops, prefix_cache=cfg.prefix_cache, cuda_graphs=cfg.cuda_graphs,
             fused_decode=cfg.fused_decode)
-        max_ctx = min(cfg.max_ctx or spec.max_positions, spec.max_positions)
+        limit = self.runner.max_positions
+        max_ctx = min(cfg.max_ctx or limit, limit)
         self.scheduler = Scheduler(
             self.runner.manager, self._run_step, max_batch=cfg.max_batch,
             max_prefill_tokens=cfg.max_prefill_tokens, max_ctx=max_ctx,

@@ -24,7 +24,7 @@ import torch
 from .loading import TORCH_DTYPES, load_model
 from .step import Runner, StepEntry, StepError
 
-DEFAULT_LIVE_REQUESTS = 8
+DEFAULT_LIVE_REQUESTS = 4
 
 
 def replay(*, model_dir, dtype: str, out_dir, max_tokens: int, lines: Iterable[str],

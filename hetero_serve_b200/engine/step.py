@@ -43,6 +43,8 @@ class StepError(RuntimeError):
 # the step reads from device memory.  It lets a decode step be launched before the host has
 # read the previous step's tokens.
 FROM_DEVICE = -1
+# the longest request of a model whose architecture names no limit (block tables are this wide)
+UNBOUNDED_MODEL_POSITIONS = 1 << 15
 HOT_SHAPE_USES = 32     # steps of one shape before it gets a second metadata block and graph
 
 
@@ -256,7 +258,9 @@ class Runner:
             self.ops.fused_decode_on = True
             self.fused = plan_fused_decode(model, self.ops, self.storage, page_size)
         self.workspace = Workspace(self.device)
-        self.max_positions = model.spec.max_positions
+        # an architecture without a limit of its own can hold what the pool can
+        self.max_positions = model.spec.max_positions or min(num_pages * page_size,
+                                                             UNBOUNDED_MODEL_POSITIONS)
         self.max_pages = [self.manager.pages_for(self.max_positions) for _ in model.cache_groups]
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         # the token each request sampled last, by state slot: what FROM_DEVICE reads

@@ -163,7 +163,7 @@ def load_library():
 def _declare(lib) -> None:
     P, I, F = c_void_p, c_int, c_float
     sig = {
-        "hs_embed": [P, P, P, P, P, P, I, I, I, I, I, P, I, P, P],
+        "hs_embed": [P, P, P, P, P, P, I, I, I, I, I, P, I, F, P, P],
         "hs_layernorm": [P, P, P, P, P, I, I, F, I, P],
         "hs_linear_simt": [P, P, P, P, P, I, I, I, I, I, I, P],
         "hs_linear_tcgen05": [P, P, P, P, P, I, I, I, I, I, I, I, P, P, P, P],
@@ -183,6 +183,17 @@ def _declare(lib) -> None:
         "hs_attention_prefill": [P, P, P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, F, P, P],
         "hs_attention_prefill_tc": [P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, I, F, P, P],
         "hs_argmax": [P, P, I, I, P],
+        "hs_dyt_norm": [P, P, P, P, P, I, I, F, I, P],
+        "hs_scale": [P, ctypes.c_longlong, F, P],
+        "hs_rotary_pairs": [P, P, P, P, I, I, I, I, I, I, P],
+        "hs_grouped_linear": [P, P, P, I, I, I, I, I, I, I, I, I, P],
+        "hs_latent_append": [P, P, P, P, P, P, I, I, I, I, I, F, I, I, I, I, P, P],
+        "hs_latent_attention": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, I, I, P, P],
+        "hs_delta_prepare": [P] * 15 + [I] * 9 + [P],
+        "hs_delta_recurrence": [P] * 10 + [I] * 8 + [P],
+        "hs_delta_finish": [P, P, P, P, P, P, I, F, I, I, I, I, I, I, I, I, P],
+        "hs_moe_route": [P, P, P, P, P, I, I, I, I, I, I, I, P],
+        "hs_moe_experts": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, F, I, P],
         "hs_sample": [P, P, P, P, P, P, P, I, I, P, P, P, P],
     }
     for name, argtypes in sig.items():
@@ -341,8 +352,8 @@ class CudaOps:
         self.lib.hs_set_pdl(int(self._pdl))
 
     # -- embedding and norm -------------------------------------------------
-    def embed(self, x, ids, pos, req, wte, wpe, status, feedback=None):
-        """x[t] = wte[ids[t]] (+ wpe[pos[t]]); rows with req[t] < 0 become zero.  With
+    def embed(self, x, ids, pos, req, wte, wpe, status, feedback=None, scale=1.0):
+        """x[t] = wte[ids[t]] * scale (+ wpe[pos[t]]); rows with req[t] < 0 become zero.  With
         ``feedback`` (int32 on the device) an id ``-(s + 1)`` stands for ``feedback[s]``."""
         _want(x, "x", torch.float32, 2)
         _want(wte, "wte", _FLOATS, 2)
@@ -364,8 +375,8 @@ class CudaOps:
         self.launches += 1
         _check(self.lib.hs_embed(_ptr(x), _ptr(ids), _ptr(pos), _ptr(req), _ptr(wte), _ptr(wpe),
                                  n, width, wte.shape[0], n_pos, _DT[wte.dtype], _ptr(feedback),
-                                 0 if feedback is None else feedback.shape[0], _ptr(status),
-                                 self._stream()), "embed")
+                                 0 if feedback is None else feedback.shape[0], float(scale),
+                                 _ptr(status), self._stream()), "embed")
 
     def layernorm(self, out, x, gamma, beta, eps, rows=None):
         """out[i] = LayerNorm(x[rows[i]] if rows is given else x[i]) * gamma + beta."""
@@ -916,6 +927,228 @@ class CudaOps:
             _ptr(tok_pos), _ptr(tok_req), _ptr(table), _ptr(logit_rows), _ptr(samp_slot),
             _ptr(plan_head), M, W, W, S, _ptr(sync), _ptr(status), int(stop_after),
             self._stream()), "decode_persistent")
+
+    # -- other norms, rotations, block-diagonal linears ---------------------------------
+    def dyt_norm(self, out, x, weight, bias, alpha, rows=None):
+        """out[i] = tanh(alpha * x[r]) * weight + bias with r = rows[i] if rows is given else i
+        (a norm without statistics)."""
+        _want(out, "out", _FLOATS, 2)
+        _want(x, "x", torch.float32, 2)
+        _want(weight, "weight", torch.float32, 1)
+        _want(bias, "bias", torch.float32, 1)
+        n, width = out.shape
+        if x.shape[1] != width or weight.shape[0] != width or bias.shape[0] != width:
+            raise KernelError("dyt_norm: widths of out, x, weight, bias differ")
+        if rows is not None:
+            _want(rows, "rows", torch.int32, 1)
+            if rows.shape[0] < n:
+                raise KernelError("dyt_norm: fewer row indices than output rows")
+        elif x.shape[0] < n:
+            raise KernelError("dyt_norm: x has fewer rows than out")
+        self.launches += 1
+        _check(self.lib.hs_dyt_norm(_ptr(out), _ptr(x), _ptr(weight), _ptr(bias), _ptr(rows), n,
+                                    width, float(alpha), _DT[out.dtype], self._stream()),
+               f"dyt_norm(width={width})")
+
+    def scale_(self, t, factor):
+        """t *= factor, in place (float32)."""
+        _want(t, "t", torch.float32)
+        self.launches += 1
+        _check(self.lib.hs_scale(_ptr(t), t.numel(), float(factor), self._stream()), "scale")
+
+    def rotary_pairs(self, buf, tok_pos, tok_req, freq, *, n_vec, vec_stride, offset, dims):
+        """Rotary positions on interleaved pairs, in place: in every row t of the float32
+        ``buf``, the ``n_vec`` vectors at columns ``offset + v * vec_stride`` have the pairs
+        (2i, 2i+1) of their first ``dims`` entries turned by ``tok_pos[t] * freq[i]``."""
+        _want(buf, "buf", torch.float32, 2)
+        _want(tok_pos, "tok_pos", torch.int32, 1)
+        _want(tok_req, "tok_req", torch.int32, 1)
+        _want(freq, "freq", torch.float32, 1)
+        n, stride = buf.shape
+        if dims % 2 or freq.shape[0] < dims // 2:
+            raise KernelError("rotary_pairs: dims must be even and freq hold dims / 2 entries")
+        if n_vec and offset + (n_vec - 1) * vec_stride + dims > stride:
+            raise KernelError("rotary_pairs: the vectors exceed the row")
+        if tok_pos.shape[0] < n or tok_req.shape[0] < n:
+            raise KernelError("rotary_pairs: fewer positions than rows")
+        self.launches += 1
+        _check(self.lib.hs_rotary_pairs(_ptr(buf), _ptr(tok_pos), _ptr(tok_req), _ptr(freq), n,
+                                        stride, n_vec, vec_stride, offset, dims, self._stream()),
+               "rotary_pairs")
+
+    def grouped_linear(self, out, a, w, *, a_offset=0, a_group_stride=None):
+        """Block-diagonal linear: ``out[t, g*n + j] = sum_k a[t, a_offset + g*a_group_stride + k]
+        * w[g, k, j]``.  ``a`` float32 (a group's input may be a slice of a wider row), ``w``
+        [groups, k, n] (k-major), ``out`` [T, groups * n] float32 or of w's type."""
+        _want(a, "a", torch.float32, 2)
+        _want(w, "w", _FLOATS, 3)
+        _want(out, "out", _FLOATS, 2)
+        groups, k, n = w.shape
+        gs = k if a_group_stride is None else int(a_group_stride)
+        T = out.shape[0]
+        if out.shape[1] != groups * n or a.shape[0] < T:
+            raise KernelError("grouped_linear: out does not fit the weights")
+        if a_offset + (groups - 1) * gs + k > a.shape[1]:
+            raise KernelError("grouped_linear: the groups' inputs exceed a's row")
+        if out.dtype != torch.float32 and out.dtype != w.dtype:
+            raise KernelError("grouped_linear: out is float32 or of the weights' type")
+        self.launches += 1
+        _check(self.lib.hs_grouped_linear(_ptr(out), _ptr(a), _ptr(w), T, a.shape[1],
+                                          int(a_offset), gs, groups, n, k, _DT[w.dtype],
+                                          _DT[out.dtype], self._stream()),
+               f"grouped_linear(groups={groups},n={n},k={k})")
+
+    # -- attention over a shared latent ---------------------------------------------------
+    def latent_append(self, pool, proj, norm_w, table, tok_pos, tok_req, *, c_offset, rank,
+                      rot_dim, eps, page_size, status):
+        """Cache row of each token: ``[rms_norm(proj[t, c_offset : +rank]) * norm_w |
+        proj[t, c_offset + rank : + rot_dim]]`` (the second part as it stands: rotate it
+        before).  ``pool`` is [pages, 1, 1, page_size, rank + rot_dim]."""
+        _want(proj, "proj", torch.float32, 2)
+        _want(pool, "pool", _FLOATS)
+        _want(norm_w, "norm_w", torch.float32, 1)
+        _want(table, "table", torch.int32, 2)
+        n = proj.shape[0]
+        W = rank + rot_dim
+        if pool.numel() % (page_size * W) or norm_w.shape[0] != rank:
+            raise KernelError("latent_append: pool or norm weight does not fit rank + rot_dim")
+        if c_offset + W > proj.shape[1] or tok_pos.shape[0] < n or tok_req.shape[0] < n:
+            raise KernelError("latent_append: rows do not fit")
+        self.launches += 1
+        _check(self.lib.hs_latent_append(_ptr(pool), _ptr(proj), _ptr(norm_w), _ptr(table),
+                                         _ptr(tok_pos), _ptr(tok_req), n, proj.shape[1],
+                                         int(c_offset), rank, rot_dim, float(eps), page_size,
+                                         pool.numel() // (page_size * W), table.shape[1],
+                                         _DT[pool.dtype], _ptr(status), self._stream()),
+               "latent_append")
+
+    def latent_attention(self, out, qa, qr, pool, table, tok_pos, tok_req, sink, *, n_heads,
+                         rank, rot_dim, qr_head_stride, qr_offset, scale, page_size, status):
+        """Causal softmax attention with a sink over cache rows ``[c (rank) | kr (rot_dim)]``
+        shared by all heads: score = (qa[t,h] . c + qr[t,h] . kr) * scale, the denominator
+        also holds exp(sink[h]); ``out[t, h] = sum_j weight_j c_j`` ([T, n_heads * rank],
+        float32).  ``qa`` [T, n_heads * rank] float32; head h's rotated query part is
+        ``qr[t, qr_offset + h * qr_head_stride : + rot_dim]``."""
+        _want(out, "out", torch.float32, 2)
+        _want(qa, "qa", torch.float32, 2)
+        _want(qr, "qr", torch.float32, 2)
+        _want(pool, "pool", _FLOATS)
+        _want(table, "table", torch.int32, 2)
+        _want(sink, "sink", torch.float32, 1)
+        n = out.shape[0]
+        W = rank + rot_dim
+        if out.shape[1] != n_heads * rank or qa.shape[1] != n_heads * rank or qa.shape[0] < n:
+            raise KernelError("latent_attention: out / qa are [T, n_heads * rank]")
+        if qr.shape[0] < n or qr_offset + (n_heads - 1) * qr_head_stride + rot_dim > qr.shape[1]:
+            raise KernelError("latent_attention: the rotated query parts exceed qr's row")
+        if pool.numel() % (page_size * W) or sink.shape[0] != n_heads:
+            raise KernelError("latent_attention: pool or sink does not fit")
+        self.launches += 1
+        _check(self.lib.hs_latent_attention(
+            _ptr(out), _ptr(qa), _ptr(qr), _ptr(pool), _ptr(table), _ptr(tok_pos), _ptr(tok_req),
+            _ptr(sink), n, n_heads, rank, rot_dim, qr.shape[1], int(qr_head_stride),
+            int(qr_offset), float(scale), page_size, pool.numel() // (page_size * W),
+            table.shape[1], _DT[pool.dtype], _ptr(status), self._stream()),
+            f"latent_attention(rank={rank},rot_dim={rot_dim})")
+
+    # -- the gated delta rule ---------------------------------------------------------------
+    @staticmethod
+    def _delta_sizes(shape):
+        return (shape["heads"], shape["kv_heads"], shape["dim"], shape["vdim"], shape["taps"],
+                shape["a_rank"], shape["g_rank"])
+
+    def delta_prepare(self, qn, kn, vv, beta, decay, proj, conv_w, a2, dt_bias, a_log, state,
+                      tok_req, req_start, req_len, req_slot, shape):
+        """From the fused projection rows ``[q | k | v | b | a | g]`` (float32): short causal
+        convolution and silu on q, k, v (history before a portion from ``state``), unit q and k
+        per head (q also times dim^-1/2), beta = sigmoid(b), decay = exp(-exp(a_log) *
+        softplus(a2 a + dt_bias)); then the convolution history in ``state`` moves on."""
+        for t, nm in ((qn, "qn"), (kn, "kn"), (vv, "vv"), (beta, "beta"), (decay, "decay"),
+                      (proj, "proj")):
+            _want(t, nm, torch.float32, 2)
+        for t, nm in ((conv_w, "conv_w"), (a2, "a2"), (dt_bias, "dt_bias"), (a_log, "a_log"),
+                      (state, "state")):
+            _want(t, nm, torch.float32)
+        H, HK, D, V, taps, ra, rg = self._delta_sizes(shape)
+        C = 2 * HK * D + H * V
+        if proj.shape[1] != C + H + ra + rg:
+            raise KernelError("delta_prepare: the projection row does not fit the sizes")
+        if state[0].numel() != H * D * V + (taps - 1) * C:
+            raise KernelError("delta_prepare: the state does not fit the sizes")
+        self.launches += 2 if taps > 1 else 1
+        _check(self.lib.hs_delta_prepare(
+            _ptr(qn), _ptr(kn), _ptr(vv), _ptr(beta), _ptr(decay), _ptr(proj), _ptr(conv_w),
+            _ptr(a2), _ptr(dt_bias), _ptr(a_log), _ptr(state), _ptr(tok_req), _ptr(req_start),
+            _ptr(req_len), _ptr(req_slot), proj.shape[0], req_start.shape[0], H, HK, D, V, taps,
+            ra, rg, self._stream()), "delta_prepare")
+
+    def delta_recurrence(self, o, state, qn, kn, vv, beta, decay, req_start, req_len, req_slot,
+                         shape):
+        """Per request and head, token after token on the float32 state S [dim, vdim]:
+        S <- decay * S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q."""
+        H, HK, D, V, taps, ra, rg = self._delta_sizes(shape)
+        for t, nm in ((o, "o"), (qn, "qn"), (kn, "kn"), (vv, "vv"), (beta, "beta"),
+                      (decay, "decay")):
+            _want(t, nm, torch.float32, 2)
+        _want(state, "state", torch.float32)
+        self.launches += 1
+        _check(self.lib.hs_delta_recurrence(
+            _ptr(o), _ptr(state), _ptr(qn), _ptr(kn), _ptr(vv), _ptr(beta), _ptr(decay),
+            _ptr(req_start), _ptr(req_len), _ptr(req_slot), req_start.shape[0], H, HK, D, V,
+            taps, ra, rg, self._stream()), f"delta_recurrence(dim={D},vdim={V})")
+
+    def delta_finish(self, out, o, proj, g2, norm_w, tok_req, eps, shape):
+        """out = o / sqrt(mean(o^2) + eps) per head * norm_w * sigmoid(g2 g)."""
+        H, HK, D, V, taps, ra, rg = self._delta_sizes(shape)
+        _want(out, "out", _FLOATS, 2)
+        _want(o, "o", torch.float32, 2)
+        _want(proj, "proj", torch.float32, 2)
+        _want(g2, "g2", torch.float32, 2)
+        _want(norm_w, "norm_w", torch.float32, 1)
+        self.launches += 1
+        _check(self.lib.hs_delta_finish(
+            _ptr(out), _ptr(o), _ptr(proj), _ptr(g2), _ptr(norm_w), _ptr(tok_req), out.shape[0],
+            float(eps), H, HK, D, V, taps, ra, rg, _DT[out.dtype], self._stream()),
+            "delta_finish")
+
+    # -- routed feed-forward ---------------------------------------------------------------
+    def moe_route(self, sel_idx, sel_w, h, w_router, tok_req, *, top, n_groups, keep):
+        """Per token: sigmoid scores of float32 router logits, group-limited choice of ``top``
+        experts, weights normalised over the chosen ones."""
+        _want(sel_idx, "sel_idx", torch.int32, 2)
+        _want(sel_w, "sel_w", torch.float32, 2)
+        _want(h, "h", _FLOATS, 2)
+        _want(w_router, "w_router", torch.float32, 2)
+        E, width = w_router.shape
+        if h.shape[1] != width or sel_idx.shape[1] != top or sel_w.shape[1] != top:
+            raise KernelError("moe_route: shapes do not fit")
+        self.launches += 1
+        _check(self.lib.hs_moe_route(_ptr(sel_idx), _ptr(sel_w), _ptr(h), _ptr(w_router),
+                                     _ptr(tok_req), sel_idx.shape[0], width, E, top, n_groups,
+                                     keep, _DT[h.dtype], self._stream()),
+               f"moe_route(experts={E},top={top},groups={n_groups},keep={keep})")
+
+    def moe_experts(self, x, y, h, w_gate, w_up, w_down, sel_idx, sel_w, tok_req, *, limit):
+        """x += sum over a token's chosen experts of weight * W_down act(W_gate h, W_up h) with
+        act(g, u) = min(g, limit) * sigmoid(1.702 min(g, limit)) * (clamp(u, +-limit) + 1).
+        Expert matrices k-major: gate / up [E, width, ff], down [E, ff, width]; ``y`` is
+        float32 scratch [T * top, ff]."""
+        _want(x, "x", torch.float32, 2)
+        _want(y, "y", torch.float32, 2)
+        _want(h, "h", _FLOATS, 2)
+        for t, nm in ((w_gate, "w_gate"), (w_up, "w_up"), (w_down, "w_down")):
+            _want(t, nm, h.dtype, 3)
+        E, width, ff = w_gate.shape
+        T, top = sel_idx.shape
+        if tuple(w_up.shape) != (E, width, ff) or tuple(w_down.shape) != (E, ff, width) \
+                or h.shape[1] != width or x.shape[1] != width or y.shape[0] < T * top \
+                or y.shape[1] != ff:
+            raise KernelError("moe_experts: shapes do not fit")
+        self.launches += 2
+        _check(self.lib.hs_moe_experts(_ptr(x), _ptr(y), _ptr(h), _ptr(w_gate), _ptr(w_up),
+                                       _ptr(w_down), _ptr(sel_idx), _ptr(sel_w), _ptr(tok_req),
+                                       T, width, ff, top, E, float(limit), _DT[h.dtype],
+                                       self._stream()), f"moe_experts(ff={ff})")
 
     # -- sampling ---------------------------------------------------------------
     def argmax(self, out, logits):

@@ -35,22 +35,25 @@ class TensorRequest:
     ``role`` decides the precision it is held in: ``matrix`` and ``table`` follow the
     compute dtype (bfloat16 or float32), ``vector`` (biases, norm parameters) is always
     float32, ``int`` is int32.  ``transpose`` asks for the stored [in, out] matrix as
-    [out, in], the layout the linear kernels read (done once, at binding).
+    [out, in], the layout the linear kernels read (done once, at binding).  ``float32`` is
+    a tensor of any rank that stays 32-bit in both precisions (a router, a decay's matrix).
     """
 
-    shape: tuple[int, ...]
+    shape: tuple[int | None, ...]     # None: this extent is read off the checkpoint's tensor
     role: str = "matrix"
     transpose: bool = False
 
 
 @dataclass(frozen=True)
 class CacheRequest:
-    """What a mixer wants kept per token: keys and values of ``kv_heads x head_dim``,
-    all of them (``window == 0``) or the last ``window`` positions."""
+    """What a mixer wants kept per token: ``planes`` rows of ``kv_heads x head_dim`` (two,
+    keys and values, for ordinary attention; one for a mixer that keeps a single shared
+    vector per token), all of them (``window == 0``) or the last ``window`` positions."""
 
     kv_heads: int
     head_dim: int
     window: int = 0
+    planes: int = 2
 
 
 class Part:

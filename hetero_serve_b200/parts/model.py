@@ -71,7 +71,21 @@ class PreNormBlock(Block):
             self.feed_forward.forward(ctx, h, x)
 
 
-_ARRANGEMENTS: dict[str, Callable[[LayerSpec], Block]] = {"pre_norm": PreNormBlock}
+class ParallelBlock(Block):
+    """One norm, both sublayers read its output:  h = norm1(x);  x += mixer(h) + feed_forward(h).
+    Each sublayer adds its share into the float32 stream."""
+
+    slots = {"norm1": "norm", "mixer": "mixer", "feed_forward": "feed_forward"}
+
+    def forward(self, ctx, x, cache):
+        h = ctx.buffer("normed", (x.shape[0], x.shape[1]), ctx.dtype)
+        self.norm1.forward(ctx, h, x)
+        self.mixer.forward(ctx, h, x, cache)
+        self.feed_forward.forward(ctx, h, x)
+
+
+_ARRANGEMENTS: dict[str, Callable[[LayerSpec], Block]] = {"pre_norm": PreNormBlock,
+                                                          "parallel": ParallelBlock}
 
 
 def register_arrangement(name: str, factory: Callable[[LayerSpec], Block], *, replace=False):
@@ -88,6 +102,7 @@ class CacheGroup:
     head_dim: int
     window: int
     entries: tuple[int, ...]        # cache entry numbers, in pool order
+    planes: int = 2                 # rows kept per token and head (keys and values: two)
 
 
 class Model:
@@ -148,14 +163,15 @@ class Model:
         for entry in sorted(entry_req):
             groups.setdefault(entry_req[entry], []).append(entry)
         self.cache_groups: list[CacheGroup] = [
-            CacheGroup(r.kv_heads, r.head_dim, r.window, tuple(es)) for r, es in groups.items()]
+            CacheGroup(r.kv_heads, r.head_dim, r.window, tuple(es), r.planes)
+            for r, es in groups.items()]
         self.entry_location: dict[int, tuple[int, int]] = {}
         for gi, g in enumerate(self.cache_groups):
             for k, e in enumerate(g.entries):
                 self.entry_location[e] = (gi, k)
 
     def kv_bytes_per_token(self, itemsize: int) -> int:
-        return sum(2 * g.kv_heads * g.head_dim * len(g.entries) * itemsize
+        return sum(g.planes * g.kv_heads * g.head_dim * len(g.entries) * itemsize
                    for g in self.cache_groups)
 
     # -- weights --------------------------------------------------------------
@@ -172,7 +188,7 @@ class Model:
                 t = t.to(device=device, dtype=dtype)
                 if req.transpose:
                     t = t.t()
-            elif req.role == "vector":
+            elif req.role in ("vector", "float32"):
                 t = t.to(device=device, dtype=torch.float32)
             elif req.role == "int":
                 t = t.to(device=device, dtype=torch.int32)

@@ -1,0 +1,75 @@
+"""A routed feed-forward (mixture of experts), and the feed-forward that is not there.
+
+Router: z = W_r h in float32, scores s = sigmoid(z).  The experts form ``groups`` equal groups
+of neighbours; a group's score is the sum of its two largest scores; only experts of the
+``keep`` best groups are eligible, and of those the ``top`` with the largest scores are chosen.
+Their weights are their scores divided by the scores' sum (+ 1e-20).  An expert is
+
+    g = min(W_gate h, limit);  u = clamp(W_up h, -limit, limit)
+    y = g * sigmoid(1.702 g) * (u + 1);   output W_down y
+
+and the layer adds the weighted sum of the chosen experts' outputs into the stream.  The
+experts' matrices are stacked once at binding, k-major, so that one kernel serves all experts.
+Routing happens on the device; cache and scheduler know nothing of it.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .base import FeedForward, TensorRequest, register_feed_forward
+
+
+class RoutedExperts(FeedForward):
+    def __init__(self, *, width: int, ff: int, experts: int, top: int, groups: int, keep: int,
+                 limit: float, router: str, expert_prefix: str):
+        if experts % groups:
+            raise ValueError(f"{experts} experts do not form {groups} equal groups")
+        if not 0 < keep <= groups or not 0 < top <= keep * (experts // groups):
+            raise ValueError("top experts must fit into the kept groups")
+        self.width, self.ff, self.E, self.top = width, ff, experts, top
+        self.groups, self.keep, self.limit = groups, keep, float(limit)
+        self.router_name, self.prefix = router, expert_prefix
+
+    def _expert(self, e: int, which: str) -> str:
+        return f"{self.prefix}{e}.{which}"
+
+    def tensor_requests(self):
+        req = {self.router_name: TensorRequest((self.E, self.width), "float32")}
+        for e in range(self.E):
+            req[self._expert(e, "gate")] = TensorRequest((self.ff, self.width), "matrix")
+            req[self._expert(e, "up")] = TensorRequest((self.ff, self.width), "matrix")
+            req[self._expert(e, "down")] = TensorRequest((self.width, self.ff), "matrix")
+        return req
+
+    def bind(self, tensors):
+        self.w_router = tensors[self.router_name]
+
+        def stack(which):          # [E, in, out]: the k index of a product runs slowest
+            return torch.stack([tensors[self._expert(e, which)].t()
+                                for e in range(self.E)]).contiguous()
+        self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
+
+    def forward(self, ctx, h, x):
+        ops, T = ctx.ops, h.shape[0]
+        idx = ctx.buffer("route_idx", (T, self.top), torch.int32)
+        wts = ctx.buffer("route_w", (T, self.top), torch.float32)
+        ops.moe_route(idx, wts, h, self.w_router, ctx.tok_req, top=self.top,
+                      n_groups=self.groups, keep=self.keep)
+        y = ctx.buffer("expert_act", (T * self.top, self.ff), torch.float32)
+        ops.moe_experts(x, y, h, self.w_gate, self.w_up, self.w_down, idx, wts, ctx.tok_req,
+                        limit=self.limit)
+
+
+class NoFeedForward(FeedForward):
+    """A layer without a feed-forward: adds nothing."""
+
+    def __init__(self, **_):
+        pass
+
+    def forward(self, ctx, h, x, norm=None):
+        return None
+
+
+register_feed_forward("routed_experts", RoutedExperts)
+register_feed_forward("none", NoFeedForward)

@@ -89,7 +89,7 @@ class ModelSpec:
     name: str
     vocab_size: int
     width: int
-    max_positions: int
+    max_positions: int | None     # None: the architecture sets no limit (the cache pool does)
     embedding: PartSpec
     position: PartSpec
     layers: tuple[LayerSpec, ...]

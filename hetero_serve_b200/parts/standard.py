@@ -46,8 +46,12 @@ class NoPositions(PositionEncoding):
 
 
 class TokenEmbedding(Embedding):
-    def __init__(self, *, vocab_size: int, width: int, table: str):
+    """x = table[token] * scale (+ the position table's row); ``scale`` is 1 unless the
+    architecture multiplies its embeddings."""
+
+    def __init__(self, *, vocab_size: int, width: int, table: str, scale: float = 1.0):
         self.vocab, self.width, self.name = vocab_size, width, table
+        self.scale = float(scale)
         self.table = None
 
     def tensor_requests(self):
@@ -57,10 +61,13 @@ class TokenEmbedding(Embedding):
         self.table = tensors[self.name]
 
     def forward(self, ctx, x, position):
+        more = {"scale": self.scale} if self.scale != 1.0 else {}
         ctx.ops.embed(x, ctx.tok_ids, ctx.tok_pos, ctx.tok_req, self.table,
-                      position.embedding_table(), ctx.status, feedback=ctx.feedback)
+                      position.embedding_table(), ctx.status, feedback=ctx.feedback, **more)
 
     def fused_decode_params(self):
+        if self.scale != 1.0:
+            return None
         return dict(table=self.table, width=self.width)
 
 
@@ -225,8 +232,9 @@ class LinearHead(Head):
     """logits = h @ W^T in float32, W being [vocab, width]: the token table itself when the
     head is tied (heteroserve/model/weights.py:40-43, torch_engine.py:86-87)."""
 
-    def __init__(self, *, vocab_size: int, width: int, weight: str):
+    def __init__(self, *, vocab_size: int, width: int, weight: str, scale: float = 1.0):
         self.vocab, self.width, self.name = vocab_size, width, weight
+        self.scale = float(scale)          # logits = (h @ W^T) * scale
         self.weight = None
 
     def tensor_requests(self):
@@ -238,7 +246,7 @@ class LinearHead(Head):
     def forward(self, ctx, logits, h):
         # a step that samples and whose rows all take the argmax: the few-row kernel picks the
         # tokens while it streams the table (and stores the status word behind them)
-        fused = getattr(ctx.ops, "linear_argmax", None)
+        fused = getattr(ctx.ops, "linear_argmax", None) if self.scale == 1.0 else None
         if fused is not None and getattr(ctx, "sampling", False) \
                 and getattr(ctx, "greedy_only", False):
             tokens = ctx.buffer(getattr(ctx, "tokens_name", "sampled"), (logits.shape[0] + 1,), torch.int32)
@@ -247,8 +255,12 @@ class LinearHead(Head):
                 ctx.fused_tokens = tokens
                 return
         ctx.ops.linear(logits, h, self.weight)
+        if self.scale != 1.0:
+            ctx.ops.scale_(logits, self.scale)
 
     def fused_decode_params(self):
+        if self.scale != 1.0:
+            return None
         return dict(weight=self.weight, vocab=self.vocab, width=self.width)
 
 

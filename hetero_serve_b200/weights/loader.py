@@ -68,8 +68,10 @@ def check_tensors(where, tensors: Mapping[str, torch.Tensor], requests) -> None:
     for n, req in requests.items():
         if n in tensors:
             t = tensors[n]
-            if tuple(t.shape) != tuple(req.shape):
-                wrong[n] = (tuple(t.shape), tuple(req.shape))
+            want = tuple(req.shape)           # None: an extent the tensor itself decides
+            if len(t.shape) != len(want) or any(w is not None and w != g
+                                                 for g, w in zip(t.shape, want)):
+                wrong[n] = (tuple(t.shape), want)
             if req.role != "int" and not t.dtype.is_floating_point:
                 other.append(f"wrong type: {n} is {t.dtype}, expected a floating-point tensor")
     if missing or unexpected or wrong or other:

@@ -28,7 +28,7 @@ class PlainOps:
     def __init__(self, compute_dtype=torch.float64):
         self.cd = compute_dtype
 
-    def embed(self, x, ids, pos, req, wte, wpe, status, feedback=None):
+    def embed(self, x, ids, pos, req, wte, wpe, status, feedback=None, scale=1.0):
         n = x.shape[0]
         for t in range(n):
             if int(req[t]) < 0:
@@ -37,7 +37,7 @@ class PlainOps:
             tok = int(ids[t])
             if tok < 0 and feedback is not None:
                 tok = int(feedback[-(tok + 1)])
-            row = wte[tok].to(self.cd)
+            row = wte[tok].to(self.cd) * scale
             if wpe is not None:
                 row = row + wpe[int(pos[t])].to(self.cd)
             x[t] = row.to(x.dtype)
@@ -124,3 +124,171 @@ class PlainOps:
             out[r] = sample_token(logits[r].cpu(), float(temperature[r]), int(top_k[r]), u)
             if feedback is not None and int(feedback_slot[r]) >= 0:
                 feedback[int(feedback_slot[r])] = out[r]
+
+    # -- twins of the kernels of the other parts (norm without statistics, rotary pairs,
+    #    block-diagonal linear, attention over a shared latent, gated delta rule, routed
+    #    experts) ------------------------------------------------------------------------
+    def dyt_norm(self, out, x, weight, bias, alpha, rows=None):
+        n = out.shape[0]
+        src = x[rows[:n].long()] if rows is not None else x[:n]
+        v = torch.tanh(alpha * src.to(self.cd)) * weight.to(self.cd) + bias.to(self.cd)
+        out.copy_(v.to(out.dtype))
+
+    def scale_(self, t, factor):
+        t.mul_(factor)
+
+    def rotary_pairs(self, buf, tok_pos, tok_req, freq, *, n_vec, vec_stride, offset, dims):
+        half = dims // 2
+        f = freq[:half].to(self.cd)
+        for t in range(buf.shape[0]):
+            if int(tok_req[t]) < 0:
+                continue
+            ang = float(tok_pos[t]) * f
+            c, s = torch.cos(ang), torch.sin(ang)
+            for v in range(n_vec):
+                lo = offset + v * vec_stride
+                seg = buf[t, lo:lo + dims].to(self.cd)
+                a, b = seg[0::2].clone(), seg[1::2].clone()
+                seg[0::2] = a * c - b * s
+                seg[1::2] = b * c + a * s
+                buf[t, lo:lo + dims] = seg.to(buf.dtype)
+
+    def grouped_linear(self, out, a, w, *, a_offset=0, a_group_stride=None):
+        groups, k, n = w.shape
+        gs = k if a_group_stride is None else a_group_stride
+        T = out.shape[0]
+        for g in range(groups):
+            lo = a_offset + g * gs
+            v = a[:T, lo:lo + k].to(self.cd) @ w[g].to(self.cd)
+            out[:, g * n:(g + 1) * n] = v.to(out.dtype)
+
+    def latent_append(self, pool, proj, norm_w, table, tok_pos, tok_req, *, c_offset, rank,
+                      rot_dim, eps, page_size, status):
+        rows = pool.view(-1, page_size, rank + rot_dim)
+        for t in range(proj.shape[0]):
+            r = int(tok_req[t])
+            if r < 0:
+                continue
+            p = int(tok_pos[t])
+            page = int(table[r, p // page_size])
+            c = proj[t, c_offset:c_offset + rank].to(self.cd)
+            c = c / torch.sqrt((c * c).mean() + eps) * norm_w.to(self.cd)
+            rows[page, p % page_size, :rank] = c.to(pool.dtype)
+            rows[page, p % page_size, rank:] = proj[t, c_offset + rank:c_offset + rank + rot_dim
+                                                    ].to(pool.dtype)
+
+    def latent_attention(self, out, qa, qr, pool, table, tok_pos, tok_req, sink, *, n_heads,
+                         rank, rot_dim, qr_head_stride, qr_offset, scale, page_size, status):
+        rows = pool.view(-1, page_size, rank + rot_dim)
+        scale32 = float(torch.tensor(scale, dtype=torch.float32))
+        for t in range(out.shape[0]):
+            r = int(tok_req[t])
+            if r < 0:
+                out[t] = 0
+                continue
+            p = int(tok_pos[t])
+            js = torch.arange(0, p + 1)
+            keys = rows[table[r, js // page_size].long(), js % page_size].to(self.cd)
+            c, kr = keys[:, :rank], keys[:, rank:]
+            for h in range(n_heads):
+                qh = qa[t, h * rank:(h + 1) * rank].to(self.cd)
+                lo = qr_offset + h * qr_head_stride
+                s = (c @ qh + kr @ qr[t, lo:lo + rot_dim].to(self.cd)) * scale32
+                top = torch.maximum(s.max(), sink[h].to(self.cd))
+                e = torch.exp(s - top)
+                den = e.sum() + torch.exp(sink[h].to(self.cd) - top)
+                out[t, h * rank:(h + 1) * rank] = ((e / den) @ c).to(out.dtype)
+
+    def delta_prepare(self, qn, kn, vv, beta, decay, proj, conv_w, a2, dt_bias, a_log, state,
+                      tok_req, req_start, req_len, req_slot, shape):
+        H, HK, D, V = shape["heads"], shape["kv_heads"], shape["dim"], shape["vdim"]
+        taps, ra = shape["taps"], shape["a_rank"]
+        C = 2 * HK * D + H * V
+        hist = taps - 1
+        cw = conv_w.to(self.cd)
+        for r in range(req_start.shape[0]):
+            n, first = int(req_len[r]), int(req_start[r])
+            if n <= 0:
+                continue
+            st = state[int(req_slot[r])]
+            old = st[H * D * V:].view(hist, C).to(self.cd) if hist else torch.zeros(0, C)
+            xs = torch.cat([old, proj[first:first + n, :C].to(self.cd)])      # [hist + n, C]
+            for l in range(n):
+                t = first + l
+                y = (xs[l:l + taps] * cw.T).sum(0)
+                y = y * torch.sigmoid(y)
+                q = y[:HK * D].view(HK, D)
+                k = y[HK * D:2 * HK * D].view(HK, D)
+                q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * D ** -0.5
+                k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+                qn[t] = q.reshape(-1).to(qn.dtype)
+                kn[t] = k.reshape(-1).to(kn.dtype)
+                vv[t] = y[2 * HK * D:].to(vv.dtype)
+                row = proj[t].to(self.cd)
+                beta[t] = torch.sigmoid(row[C:C + H]).to(beta.dtype)
+                z = a2.to(self.cd) @ row[C + H:C + H + ra] + dt_bias.to(self.cd)
+                sp = torch.where(z > 30, z, torch.log1p(torch.exp(torch.clamp(z, max=30))))
+                rate = torch.exp(a_log.to(self.cd)).repeat_interleave(D)
+                decay[t] = torch.exp(-rate * sp).to(decay.dtype)
+            if hist:
+                st[H * D * V:] = xs[n:n + hist].reshape(-1).to(st.dtype)
+
+    def delta_recurrence(self, o, state, qn, kn, vv, beta, decay, req_start, req_len, req_slot,
+                         shape):
+        H, HK, D, V = shape["heads"], shape["kv_heads"], shape["dim"], shape["vdim"]
+        for r in range(req_start.shape[0]):
+            n, first = int(req_len[r]), int(req_start[r])
+            if n <= 0:
+                continue
+            st = state[int(req_slot[r])]
+            S = st[:H * D * V].view(H, D, V).to(self.cd)
+            for t in range(first, first + n):
+                for h in range(H):
+                    kh = h // (H // HK)
+                    k = kn[t, kh * D:(kh + 1) * D].to(self.cd)
+                    q = qn[t, kh * D:(kh + 1) * D].to(self.cd)
+                    S[h] = decay[t, h * D:(h + 1) * D].to(self.cd).view(D, 1) * S[h]
+                    u = beta[t, h].to(self.cd) * (vv[t, h * V:(h + 1) * V].to(self.cd) - S[h].T @ k)
+                    S[h] = S[h] + torch.outer(k, u)
+                    o[t, h * V:(h + 1) * V] = (S[h].T @ q).to(o.dtype)
+            st[:H * D * V] = S.reshape(-1).to(st.dtype)
+
+    def delta_finish(self, out, o, proj, g2, norm_w, tok_req, eps, shape):
+        H, HK, D, V = shape["heads"], shape["kv_heads"], shape["dim"], shape["vdim"]
+        ra, rg = shape["a_rank"], shape["g_rank"]
+        g_off = 2 * HK * D + H * V + H + ra
+        T = out.shape[0]
+        v = o[:T].to(self.cd).view(T, H, V)
+        v = v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps) * norm_w.to(self.cd)
+        gate = torch.sigmoid(proj[:T, g_off:g_off + rg].to(self.cd) @ g2.to(self.cd).T)
+        out.copy_((v.view(T, H * V) * gate).to(out.dtype))
+
+    def moe_route(self, sel_idx, sel_w, h, w_router, tok_req, *, top, n_groups, keep):
+        E = w_router.shape[0]
+        per = E // n_groups
+        for t in range(sel_idx.shape[0]):
+            if int(tok_req[t]) < 0:
+                continue
+            s = torch.sigmoid(w_router.to(self.cd) @ h[t].to(self.cd))
+            gs = torch.topk(s.view(n_groups, per), min(2, per), dim=-1).values.sum(-1)
+            kept = torch.zeros(n_groups, dtype=torch.bool)
+            kept[torch.topk(gs, keep).indices] = True
+            masked = torch.where(kept.repeat_interleave(per), s, torch.full_like(s, -1.0))
+            idx = torch.topk(masked, top).indices
+            sel_idx[t] = idx.to(torch.int32)
+            sel_w[t] = (s[idx] / (s[idx].sum() + 1e-20)).to(sel_w.dtype)
+
+    def moe_experts(self, x, y, h, w_gate, w_up, w_down, sel_idx, sel_w, tok_req, *, limit):
+        T, top = sel_idx.shape
+        for t in range(T):
+            if int(tok_req[t]) < 0:
+                continue
+            hv = h[t].to(self.cd)
+            add = torch.zeros(x.shape[1], dtype=self.cd)
+            for k in range(top):
+                e = int(sel_idx[t, k])
+                g = torch.clamp(hv @ w_gate[e].to(self.cd), max=limit)
+                u = torch.clamp(hv @ w_up[e].to(self.cd), min=-limit, max=limit)
+                act = g * torch.sigmoid(1.702 * g) * (u + 1.0)
+                add = add + sel_w[t, k].to(self.cd) * (act @ w_down[e].to(self.cd))
+            x[t] = (x[t].to(self.cd) + add).to(x.dtype)
