@@ -89,3 +89,14 @@ def tiny(request, tiny_models):
 # float32: kernels accumulate in float32 over at most a few hundred terms.
 # bfloat16: activations between kernels are rounded to 8 bits of mantissa.
 TOL = {"float32": 2e-5, "bfloat16": 2.5e-2}
+
+
+@pytest.fixture(scope="session")
+def pedorax_cases(tmp_path_factory):
+    import pedorax_cases as pc
+    return pc.make_cases(tmp_path_factory)
+
+
+@pytest.fixture(params=["case_a", "case_b"])
+def pedorax_case(request, pedorax_cases):
+    return pedorax_cases[request.param]

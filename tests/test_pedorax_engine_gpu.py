@@ -1,0 +1,159 @@
+"""Pedorax through the engine on the GPU: the step function, the paged latent cache, the state
+slots and the CUDA kernels against the plain implementation (tests/plain_pedorax.py), in both
+precisions; then greedy generation through the Python entry point and its scheduler."""
+
+import io
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import pedorax_cases as pc
+import plain_pedorax
+import traces
+from hetero_serve_b200.engine.loading import load_model
+from hetero_serve_b200.engine.replay import replay
+from hetero_serve_b200.engine.step import Runner, StepEntry
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+# relative root-mean-square error of a row of logits (see pedorax_cases.rms_error): float32 sums
+# of a few hundred terms; bfloat16 rounds the normed rows and the cache rows to 8 bits
+TOL = {"float32": 2e-5, "bfloat16": 6e-2}
+
+
+def _replay(case, dtype, steps, tmp_path, max_tokens, **kw):
+    out = tmp_path / f"out_{dtype}"
+    out.mkdir(exist_ok=True)
+    assert replay(model_dir=case.dir, dtype=dtype, out_dir=out, max_tokens=max_tokens,
+                  lines=traces.lines_of(steps), report=io.StringIO(), device=DEV, **kw) == 0
+    return out
+
+
+def _worst(case, dtype, out, index, reqs):
+    """The error that has to stay under the tolerance, where it occurs, and how many rows were
+    compared.  float32: the largest error.  bfloat16: rounding the normed rows can change which
+    expert a token picks where two router scores nearly tie, and such a token (and little
+    behind it) is then far from the plain model; so one row in twenty may be, and the
+    twentieth-largest-fraction error and three times the median have to stay under it."""
+    got = traces.collect(out, index, case.vocab)
+    errs = sorted(((pc.rms_error(torch.as_tensor(row), case.logits(reqs[rid], dtype)[p]),
+                    (rid, p)) for (rid, p), row in got.items()), reverse=True)
+    if dtype == "float32":
+        return errs[0][0], errs[0][1], len(errs)
+    k = len(errs) // 20
+    return max(errs[k][0], 3 * errs[len(errs) // 2][0]), errs[k][1], len(errs)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("driver", ["whole", "tail", "portions"])
+def test_cuts_agree_with_the_plain_model(pedorax_case, tmp_path, dtype, driver):
+    reqs = {f"r{i}": pedorax_case.tokens(n, 150 + i) for i, n in enumerate((1, 2, 23, 70, 131))}
+    if driver == "whole":
+        steps, index = traces.whole(reqs)
+    elif driver == "tail":
+        steps, index = traces.tail_one_by_one(reqs, tail=40)
+    else:
+        steps, index = traces.portions(reqs, sizes=(24, 7, 2, 16, 3, 2, 31, 5, 2, 9))
+    out = _replay(pedorax_case, dtype, steps, tmp_path, max_tokens=192)
+    err, where, n = _worst(pedorax_case, dtype, out, index, reqs)
+    assert n > 4 and err < TOL[dtype], (err, where)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixed_batches_reuse_pages_and_slots(pedorax_case, tmp_path, dtype):
+    reqs = {f"r{i}": pedorax_case.tokens(n, 170 + i) for i, n in
+            enumerate((90, 9, 64, 23, 70, 3, 55, 31, 2))}
+    steps, index, peak = traces.mixed(reqs, seed=2)
+    out = _replay(pedorax_case, dtype, steps, tmp_path, max_tokens=peak, max_requests=4)
+    err, where, n = _worst(pedorax_case, dtype, out, index, reqs)
+    assert n > 40 and err < TOL[dtype], (err, where)
+
+
+def _runner(case, dtype="float32", pages=16, slots=4, **kw):
+    model, _ = load_model(case.dir, dtype, DEV)
+    return Runner(model, num_pages=pages, page_size=16, max_requests=slots, dtype=model.dtype,
+                  device=DEV, **kw)
+
+
+def test_a_request_alone_and_in_a_batch(pedorax_case):
+    """The logits of a request do not depend on its neighbours in the batch, nor on the slot
+    and pages it got."""
+    case = pedorax_case
+    a, b, c = case.tokens(45, 1), case.tokens(20, 2), case.tokens(33, 3)
+    alone = _runner(case)
+    want = alone.step([StepEntry("a", a[:30], want=[29])]).logits.clone()
+    want2 = alone.step([StepEntry("a", a[30:], want=[0, 14])]).logits.clone()
+    rn = _runner(case)
+    rn.step([StepEntry("c", c)])                  # takes the first slot and pages
+    got = rn.step([StepEntry("b", b[:7]), StepEntry("a", a[:30], want=[29]),
+                   StepEntry("c", [5])]).logits.clone()
+    rn.close("c")
+    got2 = rn.step([StepEntry("a", a[30:], want=[0, 14]), StepEntry("b", b[7:])]).logits
+    assert (got - want).abs().max() < 1e-5 and (got2 - want2).abs().max() < 1e-5
+    assert pc.rms_error(got2[1].cpu(), case.logits(a)[44]) < TOL["float32"]
+
+
+def test_freed_slots_and_pages_start_clean(pedorax_cases):
+    case = pedorax_cases["case_a"]
+    rn = _runner(case, pages=5, slots=1)
+    for seed, n in ((4, 70), (5, 41), (6, 80)):
+        t = case.tokens(n, seed)
+        rn.step([StepEntry("x", t[:n // 2])])
+        res = rn.step([StepEntry("x", t[n // 2:], want=[n - n // 2 - 1])])
+        assert pc.rms_error(res.logits[0].cpu(), case.logits(t)[n - 1]) < TOL["float32"], seed
+        rn.close("x")
+    rn.manager.check()
+
+
+def test_long_decoding(pedorax_cases):
+    """Far more single-token steps than the convolution's history and several pages long."""
+    case = pedorax_cases["case_a"]
+    t = case.tokens(260, 9)
+    rn = _runner(case, pages=20)
+    rn.step([StepEntry("d", t[:12])])
+    want = case.logits(t)
+    for i in range(12, 260):
+        res = rn.step([StepEntry("d", [t[i]], want=[0])])
+        if i % 31 == 0 or i > 250:
+            assert pc.rms_error(res.logits[0].cpu(), want[i]) < TOL["float32"], i
+
+
+def _greedy(case, prompt, n, dtype="float32"):
+    w = case.plain if dtype == "float32" else case.plain_bf16
+    toks, out, margins = list(prompt), [], []
+    for _ in range(n):
+        row = plain_pedorax.forward(case.config, w, toks)[-1]
+        top = torch.topk(row, 2).values
+        margins.append(float(top[0] - top[1]))
+        out.append(int(row.argmax()))
+        toks.append(out[-1])
+    return out, margins
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_greedy_generation_through_the_entry_point(pedorax_case, graphs):
+    """Prompts of unequal length, cut into portions by a small token budget, decoded side by
+    side by the scheduler (with and without CUDA graphs: the recurrent state must survive the
+    capture); the tokens are the plain model's greedy tokens."""
+    from hetero_serve_b200 import LLMEngine
+    case = pedorax_case
+    prompts = [case.tokens(n, 200 + n) for n in (37, 5, 18)]
+    eng = LLMEngine(case.dir, dtype="float32", num_blocks=24, max_batch=4, max_prefill_tokens=16,
+                    policy="mixed", cuda_graphs=graphs, device=DEV)
+    got = eng.generate(prompts, max_new_tokens=10)
+    for p, g in zip(prompts, got):
+        want, margins = _greedy(case, p, 10)
+        for i, (a, b, m) in enumerate(zip(g, want, margins)):
+            if m < 1e-3:
+                break                                         # a close call: stop comparing
+            assert a == b, (len(p), i, g, want)
+    eng.runner.manager.check()
+
+
+def test_command_line_runs_a_preset():
+    out = subprocess.run([sys.executable, "-m", "hetero_serve_b200", "--model", "pedorax-tiny",
+                          "--random-prompts", "2:12", "--max-new-tokens", "4"],
+                         capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
