@@ -594,6 +594,90 @@ def run_ours(args):
     return 0
 
 
+def run_compare(args):
+    """Another architecture beside GPT-2 at equal width, depth and vocabulary (random weights):
+    prefill of 2 x 1,024 tokens and decode at batch 8 over a context of about 600, each through
+    the engine with CUDA graphs; then one eager prefill step and one eager decode step with a
+    stopwatch around every operation, as fractions of each operation's roofline."""
+    import torch
+    from hetero_serve_b200.config import preset
+    from hetero_serve_b200.engine import Runner, StepEntry, load_model
+    from hetero_serve_b200.kernels import CudaOps
+    from hetero_serve_b200.kernels.compare import TimedOps, fractions
+    from hetero_serve_b200.weights import write_model_dir
+
+    if not torch.cuda.is_available():
+        print(json.dumps({"impl": "ours", "error": "no CUDA device: this engine has no CPU path"}))
+        return 1
+    pk, pk_src = peaks()
+    dtype = args.dtype
+    tdt = torch.bfloat16 if dtype == "bfloat16" else torch.float32
+    if dtype == "bfloat16":
+        peak = pk["bf16_tflops"]
+    else:
+        props = torch.cuda.get_device_properties(0)
+        peak = props.multi_processor_count * 128 * 2 * props.clock_rate * 1e3 / 1e12
+    batch, ctx0, k_steps = 8, 576, 32
+    out = {"impl": "ours", "compare": [], "dtype": dtype, "peaks": pk_src,
+           "peak_tflops": round(peak, 1), "hbm_gbs": pk["hbm_gbs"],
+           "workload": {"prefill": "2 x 1024 tokens", "decode": f"batch {batch}, context "
+                        f"{ctx0}..{ctx0 + k_steps}", "data": "synthetic, random weights"}}
+    for name in [n for n in args.compare.split(",") if n]:
+        new = preset(name)
+        width, n_layers, vocab = new["width"], len(new["layers"]), new["vocab"]
+        twin = {"architectures": ["GPT2LMHeadModel"], "model_type": "gpt2", "n_layer": n_layers,
+                "n_embd": width, "n_head": max(1, width // 64), "n_inner": 4 * width,
+                "vocab_size": vocab, "n_positions": 2048, "layer_norm_epsilon": 1e-5,
+                "activation_function": "gelu_new", "tie_word_embeddings": True,
+                "eos_token_id": None}
+        row = {"size": name, "width": width, "layers": n_layers, "vocab": vocab}
+        for label, cfg in ((name, new), ("gpt2-equal", twin)):
+            with tempfile.TemporaryDirectory(prefix="hsb200-cmp-") as d:
+                write_model_dir(d, cfg, seed=0, dtype=dtype)
+                model, _ = load_model(d, dtype, "cuda:0")
+                runner = Runner(model, num_pages=1024, page_size=16, max_requests=64, dtype=tdt,
+                                device="cuda:0", prefix_cache=False, cuda_graphs=True)
+                pre_ms, _single = time_prefill(runner, torch, 2, 1024, vocab, 5)
+                dec_ms, launches, _pw = time_decode(runner, torch, batch,
+                                                    [(ctx0, k_steps, 3)], 4, vocab, 1, "c")
+                del runner
+                ops = TimedOps(CudaOps("cuda:0"))
+                eager = Runner(model, num_pages=512, page_size=16, max_requests=16, dtype=tdt,
+                               device="cuda:0", prefix_cache=False, cuda_graphs=False, ops=ops)
+                g = torch.Generator().manual_seed(3)
+                tables = {}
+                for rep in range(3):                      # the third run is the one that counts
+                    prompts = torch.randint(0, vocab, (2, 1024), generator=g).tolist()
+                    ops.batch = [(0, 1024), (0, 1024)]
+                    eager.step([StepEntry(f"p{rep}_{i}", p, want=[1023])
+                                for i, p in enumerate(prompts)], sample=True)
+                    tables["prefill"] = ops.collect()
+                    for i in range(2):
+                        eager.close(f"p{rep}_{i}")
+                ids = [f"d{i}" for i in range(batch)]
+                for i in ids:
+                    eager.step([StepEntry(i, torch.randint(0, vocab, (ctx0,), generator=g).tolist())],
+                               sample=False)
+                ops.collect()
+                for rep in range(3):
+                    ops.batch = [(ctx0 + rep, 1)] * batch
+                    eager.step([StepEntry(i, [1 + rep], want=[0]) for i in ids], sample=True)
+                    tables["decode"] = ops.collect()
+                row[label] = {
+                    "prefill_ms": round(pre_ms, 3), "prefill_tok_s": round(2048 / pre_ms * 1e3, 1),
+                    "decode_ms_per_step": round(dec_ms / k_steps, 4),
+                    "decode_tok_s": round(batch * k_steps / dec_ms * 1e3, 1),
+                    "decode_launches_per_step": launches // k_steps,
+                    "weights_mb": round(model.weight_bytes() / 1e6, 1),
+                    "ops_prefill": fractions(tables["prefill"], peak, pk["hbm_gbs"]),
+                    "ops_decode": fractions(tables["decode"], peak, pk["hbm_gbs"])}
+                del eager, model, ops
+                torch.cuda.empty_cache()
+        out["compare"].append(row)
+    print(json.dumps(out))
+    return 0
+
+
 def run_kernels(args):
     """Per-kernel table: time alone with a cold L2, bytes or FLOPs, fraction of the peak."""
     import torch
@@ -810,6 +894,11 @@ def main() -> int:
     ap.add_argument("--phase-marks", dest="phase_marks", action="store_true",
                     help="print the few-row linears' own time marks inside a CUDA graph (needs a "
                          "library built with HETERO_SERVE_PHASE_MARKS=1) and exit")
+    ap.add_argument("--compare", nargs="?", const="pedorax-1k,pedorax-2k", default="",
+                    help="instead of the default workload: named configurations of another "
+                         "architecture (default pedorax-1k,pedorax-2k), each beside GPT-2 at equal "
+                         "width, depth and vocabulary: prefill and decode throughput and every "
+                         "operation of a step against its roofline")
     ap.add_argument("--one-step", dest="one_step", default="", choices=["", "decode", "prefill"],
                     help="for profilers: run a single eager step between cudaProfilerStart/Stop")
     args = ap.parse_args()
@@ -820,6 +909,8 @@ def main() -> int:
         args.warmup = 3
     if args.impl == "reference":
         return run_reference(args)
+    if args.compare:
+        return run_compare(args)
     if args.kernels:
         return run_kernels(args)
     if args.phase_marks:

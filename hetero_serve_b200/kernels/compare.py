@@ -1,0 +1,147 @@
+"""Per-operation timing of whole steps, for comparing one architecture with another.
+
+:class:`TimedOps` stands in front of a :class:`CudaOps`: every operation a step calls is
+bracketed by two CUDA events on the step's stream, and after the step the times are read and
+summed per operation name, together with the operation's algorithmic FLOPs and bytes (from the
+shapes of its arguments and the batch the caller describes).  The roofline time of an operation
+is the larger of FLOPs / peak and bytes / bandwidth; the fraction reported is roofline time over
+measured time.  Steps run eagerly (no CUDA graph), so a time includes the launch gap before the
+kernel; operations of a few microseconds are dominated by it.
+"""
+
+from __future__ import annotations
+
+from collections import defaultdict
+
+import torch
+
+
+def _nbytes(*ts) -> int:
+    return sum(t.numel() * t.element_size() for t in ts if isinstance(t, torch.Tensor))
+
+
+class TimedOps:
+    """A proxy: ``ops`` with a stopwatch around each operation."""
+
+    def __init__(self, ops):
+        object.__setattr__(self, "_ops", ops)
+        object.__setattr__(self, "_events", [])
+        object.__setattr__(self, "batch", [])          # [(start, n)] of the step being run
+
+    def __getattr__(self, name):
+        target = getattr(self._ops, name)
+        if not callable(target) or name.startswith("_") or name in _UNTIMED:
+            return target
+
+        def timed(*args, **kw):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            out = target(*args, **kw)
+            b.record()
+            self._events.append((name, a, b, _work(name, args, kw, self.batch)))
+            return out
+        return timed
+
+    def __setattr__(self, name, value):
+        if name == "batch":
+            object.__setattr__(self, name, value)
+        else:
+            setattr(self._ops, name, value)
+
+    def collect(self) -> dict:
+        """{operation: [ms, flops, bytes, calls]} since the last call; synchronises."""
+        torch.cuda.synchronize()
+        out = defaultdict(lambda: [0.0, 0, 0, 0])
+        for name, a, b, (flops, nbytes) in self._events:
+            rec = out[name]
+            rec[0] += a.elapsed_time(b)
+            rec[1] += flops
+            rec[2] += nbytes
+            rec[3] += 1
+        self._events.clear()
+        return dict(out)
+
+
+_UNTIMED = {"stream", "register_kernel", "load_extension", "attention_plan_ints",
+            "plan_attention", "make_plan", "decode_wide", "decode_splits"}
+
+
+def _contexts(batch):
+    """Sum over the step's tokens of the keys each sees, and the distinct cache rows read."""
+    seen = sum(n * start + n * (n + 1) // 2 for start, n in batch)
+    rows = sum(start + n for start, n in batch)
+    return seen, rows
+
+
+def _work(name, args, kw, batch):
+    """(FLOPs, bytes) an operation has to do, from its arguments."""
+    try:
+        if name == "linear":
+            out, a, w = args[:3]
+            res = kw.get("residual") if "residual" in kw else (args[5] if len(args) > 5 else None)
+            return 2 * a.shape[0] * a.shape[1] * w.shape[0], _nbytes(out, a, w, res)
+        if name == "norm_linear":
+            out, _h, x = args[:3]
+            w = args[6]
+            return 2 * x.shape[0] * x.shape[1] * w.shape[0], _nbytes(out, x, w)
+        if name == "linear_argmax":
+            out, a, w = args[:3]
+            return 2 * a.shape[0] * a.shape[1] * w.shape[0], _nbytes(out, a, w)
+        if name in ("layernorm", "dyt_norm"):
+            return 0, _nbytes(args[0]) + args[0].numel() * 4
+        if name == "attention_append":
+            out, qkv, pool = args[:3]
+            g = args[6]
+            seen, rows = _contexts(batch)
+            kv_row = 2 * g.n_kv_heads * g.head_dim * pool.element_size()
+            return 4 * g.n_heads * g.head_dim * seen, _nbytes(out, qkv) + rows * kv_row
+        if name == "latent_attention":
+            out, qa = args[:2]
+            pool = args[3]
+            H, R, P = kw["n_heads"], kw["rank"], kw["rot_dim"]
+            seen, rows = _contexts(batch)
+            return 2 * H * (2 * R + P) * seen, _nbytes(out, qa) + rows * (R + P) * pool.element_size()
+        if name == "grouped_linear":
+            out, a, w = args[:3]
+            groups, k, n = w.shape
+            return 2 * out.shape[0] * groups * k * n, _nbytes(out, w) + out.shape[0] * groups * k * 4
+        if name == "delta_prepare":
+            return 0, _nbytes(*args[:6])
+        if name == "delta_recurrence":
+            o, state = args[:2]
+            shape = args[-1]
+            T = o.shape[0]
+            live = len([1 for _s, n in batch if n > 0])
+            st = 2 * live * shape["heads"] * shape["dim"] * shape["vdim"] * 4
+            return 7 * T * shape["heads"] * shape["dim"] * shape["vdim"], _nbytes(*args[2:7], o) + st
+        if name == "delta_finish":
+            return 0, _nbytes(args[0], args[1])
+        if name == "moe_route":
+            h, wr = args[2], args[3]
+            return 2 * h.shape[0] * wr.shape[0] * wr.shape[1], _nbytes(h, wr)
+        if name == "moe_experts":
+            x, _y, h, wg = args[:4]
+            idx = args[6]
+            E, width, ff = wg.shape
+            pairs = idx.shape[0] * idx.shape[1]
+            touched = min(E, pairs) * 3 * width * ff * wg.element_size()
+            return 2 * pairs * 3 * width * ff, _nbytes(h) + 2 * _nbytes(x) + touched
+        if name in ("embed", "scale_", "rotary_pairs", "latent_append", "sample", "argmax",
+                    "kv_append"):
+            return 0, _nbytes(args[0])
+    except Exception:                                   # an estimate must never stop a step
+        pass
+    return 0, 0
+
+
+def fractions(table: dict, peak_tflops: float, hbm_gbs: float) -> dict:
+    """{operation: {"ms", "calls", "roof_ms", "frac", "bound"}} from :meth:`TimedOps.collect`."""
+    out = {}
+    for name, (ms, flops, nbytes, calls) in sorted(table.items(), key=lambda kv: -kv[1][0]):
+        t_f = flops / (peak_tflops * 1e12) * 1e3
+        t_b = nbytes / (hbm_gbs * 1e9) * 1e3
+        roof = max(t_f, t_b)
+        out[name] = {"ms": round(ms, 4), "calls": calls, "roof_ms": round(roof, 5),
+                     "frac": round(roof / ms, 4) if ms > 0 else None,
+                     "bound": "flops" if t_f >= t_b else "bytes"}
+    return out
