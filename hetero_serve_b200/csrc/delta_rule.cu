@@ -12,7 +12,9 @@
 //   recurrence per request and head, token after token on the float32 state S [D x V]:
 //                 S <- decay * S (row-wise);  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
 //   finish     per token and head: o / sqrt(mean(o^2) + eps) * w * sigmoid(W_g2 g)
-// Everything here is float32 whatever the model's matrix type is.
+// Everything here is float32 whatever the model's matrix type is.  The two small matrices W_a2
+// and W_g2 are held with the summed index slowest ([ra, heads x D] and [rg, heads x V]) so that
+// neighbouring threads read neighbouring weights.
 //
 // State of a slot: [heads x D x V | (taps-1) x channels] floats.
 #include "common.cuh"
@@ -83,7 +85,7 @@ delta_prepare_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __re
   const int HD = s.heads * s.D;
   for (int i = threadIdx.x; i < HD; i += blockDim.x) {
     float z = 0.f;
-    for (int k = 0; k < s.ra; ++k) z = fmaf(a2[(size_t)i * s.ra + k], row[s.a_off + k], z);
+    for (int k = 0; k < s.ra; ++k) z = fmaf(a2[(size_t)k * HD + i], row[s.a_off + k], z);
     z += dt_bias[i];
     decay[(size_t)t * HD + i] = expf(-expf(A_log[i / s.D]) * softplusf_(z));
   }
@@ -115,19 +117,31 @@ constexpr int DR_DP = 8;          // state rows a thread keeps
 constexpr int DR_THREADS = 128;
 
 // Thread (col, part) keeps rows part*DP .. part*DP+DP-1 of column col of S; the KS parts of a
-// column are neighbouring lanes and sum their shares with a butterfly.
+// column are neighbouring lanes and sum their shares with a butterfly.  The tokens' q, k, decay
+// rows (padded with zeros to KS*DP), v columns and betas come through shared memory a chunk of
+// CH tokens at a time, so that the latency of fetching them is paid once a chunk, not once a
+// token.
 __global__ void __launch_bounds__(DR_THREADS)
 delta_recurrence_kernel(float* __restrict__ o, float* __restrict__ state,
                         const float* __restrict__ qn, const float* __restrict__ kn,
                         const float* __restrict__ vv, const float* __restrict__ beta,
                         const float* __restrict__ decay, const int* __restrict__ req_start,
                         const int* __restrict__ req_len, const int* __restrict__ req_slot,
-                        DeltaShape s, int KS) {
+                        DeltaShape s, int KS, int CH) {
+  extern __shared__ __align__(16) float sm[];
   const int r = blockIdx.x, h = blockIdx.y;
   const int n = req_len[r];
   if (n <= 0) return;
+  const int Dp = KS * DR_DP;
+  const int cols = DR_THREADS / KS;
+  float* s_k = sm;
+  float* s_q = s_k + CH * Dp;
+  float* s_g = s_q + CH * Dp;
+  float* s_v = s_g + CH * Dp;
+  float* s_b = s_v + CH * cols;
   const int part = threadIdx.x % KS;
-  const int col = blockIdx.z * (DR_THREADS / KS) + threadIdx.x / KS;
+  const int lc = threadIdx.x / KS;
+  const int col = blockIdx.z * cols + lc;
   const bool col_ok = col < s.V;
   const int kh = h / (s.heads / s.kv_heads);
   const int d0 = part * DR_DP;
@@ -138,44 +152,52 @@ delta_recurrence_kernel(float* __restrict__ o, float* __restrict__ state,
     st[i] = (col_ok && d0 + i < s.D) ? S[(size_t)(d0 + i) * s.V + col] : 0.f;
   const int QK = s.kv_heads * s.D, HV = s.heads * s.V, HD = s.heads * s.D;
   const int first = req_start[r];
-  float kk[DR_DP], qq[DR_DP], gg[DR_DP], vc, b;
-  auto fetch = [&](int row, float* k_, float* q_, float* g_, float& v_, float& b_) {
-#pragma unroll
-    for (int i = 0; i < DR_DP; ++i) {
-      const bool ok = d0 + i < s.D;
-      k_[i] = ok ? kn[(size_t)row * QK + kh * s.D + d0 + i] : 0.f;
-      q_[i] = ok ? qn[(size_t)row * QK + kh * s.D + d0 + i] : 0.f;
-      g_[i] = ok ? decay[(size_t)row * HD + h * s.D + d0 + i] : 0.f;
+  for (int c0 = 0; c0 < n; c0 += CH) {
+    const int nc = min(CH, n - c0);
+    __syncthreads();                               // the chunk before has been used
+    for (int i = threadIdx.x; i < nc * Dp; i += DR_THREADS) {
+      const int tt = i / Dp, d = i - tt * Dp;
+      const size_t row = first + c0 + tt;
+      const bool ok = d < s.D;
+      s_k[i] = ok ? kn[row * QK + kh * s.D + d] : 0.f;
+      s_q[i] = ok ? qn[row * QK + kh * s.D + d] : 0.f;
+      s_g[i] = ok ? decay[row * HD + h * s.D + d] : 0.f;
     }
-    v_ = col_ok ? vv[(size_t)row * HV + h * s.V + col] : 0.f;
-    b_ = beta[(size_t)row * s.heads + h];
-  };
-  fetch(first, kk, qq, gg, vc, b);
-  for (int i = 0; i < n; ++i) {
-    const int row = first + i;
-    float k2[DR_DP], q2[DR_DP], g2[DR_DP], v2 = 0.f, b2 = 0.f;
-    if (i + 1 < n) fetch(row + 1, k2, q2, g2, v2, b2);     // the next token's, while this one runs
-    float dot = 0.f;
-#pragma unroll
-    for (int j = 0; j < DR_DP; ++j) {
-      st[j] *= gg[j];
-      dot = fmaf(st[j], kk[j], dot);
+    for (int i = threadIdx.x; i < nc * cols; i += DR_THREADS) {
+      const int tt = i / cols, cc = i - tt * cols;
+      const int cg = blockIdx.z * cols + cc;
+      s_v[i] = cg < s.V ? vv[(size_t)(first + c0 + tt) * HV + h * s.V + cg] : 0.f;
     }
-    for (int off = 1; off < KS; off <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
-    const float u = b * (vc - dot);
-    float out = 0.f;
+    if (threadIdx.x < nc) s_b[threadIdx.x] = beta[(size_t)(first + c0 + threadIdx.x) * s.heads + h];
+    __syncthreads();
+    for (int tt = 0; tt < nc; ++tt) {
+      const float4* k4 = (const float4*)(s_k + tt * Dp + d0);
+      const float4* q4 = (const float4*)(s_q + tt * Dp + d0);
+      const float4* g4 = (const float4*)(s_g + tt * Dp + d0);
+      float kk[DR_DP], qq[DR_DP], gg[DR_DP];
 #pragma unroll
-    for (int j = 0; j < DR_DP; ++j) {
-      st[j] = fmaf(kk[j], u, st[j]);
-      out = fmaf(st[j], qq[j], out);
-    }
-    for (int off = 1; off < KS; off <<= 1) out += __shfl_xor_sync(0xffffffffu, out, off);
-    if (part == 0 && col_ok) o[(size_t)row * HV + h * s.V + col] = out;
-    if (i + 1 < n) {
+      for (int j = 0; j < DR_DP / 4; ++j) {
+        const float4 a = k4[j], b = q4[j], c = g4[j];
+        kk[4 * j] = a.x; kk[4 * j + 1] = a.y; kk[4 * j + 2] = a.z; kk[4 * j + 3] = a.w;
+        qq[4 * j] = b.x; qq[4 * j + 1] = b.y; qq[4 * j + 2] = b.z; qq[4 * j + 3] = b.w;
+        gg[4 * j] = c.x; gg[4 * j + 1] = c.y; gg[4 * j + 2] = c.z; gg[4 * j + 3] = c.w;
+      }
+      float dot = 0.f;
 #pragma unroll
-      for (int j = 0; j < DR_DP; ++j) { kk[j] = k2[j]; qq[j] = q2[j]; gg[j] = g2[j]; }
-      vc = v2;
-      b = b2;
+      for (int j = 0; j < DR_DP; ++j) {
+        st[j] *= gg[j];
+        dot = fmaf(st[j], kk[j], dot);
+      }
+      for (int off = 1; off < KS; off <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+      const float u = s_b[tt] * (s_v[tt * cols + lc] - dot);
+      float out = 0.f;
+#pragma unroll
+      for (int j = 0; j < DR_DP; ++j) {
+        st[j] = fmaf(kk[j], u, st[j]);
+        out = fmaf(st[j], qq[j], out);
+      }
+      for (int off = 1; off < KS; off <<= 1) out += __shfl_xor_sync(0xffffffffu, out, off);
+      if (part == 0 && col_ok) o[(size_t)(first + c0 + tt) * HV + h * s.V + col] = out;
     }
   }
 #pragma unroll
@@ -201,9 +223,9 @@ delta_finish_kernel(TO* __restrict__ out, const float* __restrict__ o,
     ss = warp_sum(ss);
     const float inv = 1.0f / sqrtf(ss / (float)s.V + eps);
     for (int e = lane; e < s.V; e += 32) {
-      const float* grow = g2 + (size_t)(h * s.V + e) * s.rg;
+      const float* gcol = g2 + (size_t)h * s.V + e;
       float z = 0.f;
-      for (int k = 0; k < s.rg; ++k) z = fmaf(grow[k], gin[k], z);
+      for (int k = 0; k < s.rg; ++k) z = fmaf(gcol[(size_t)k * HV], gin[k], z);
       out[(size_t)t * HV + h * s.V + e] = from_f<TO>(src[e] * inv * norm_w[e] * sigmoidf_(z));
     }
   }
@@ -275,9 +297,11 @@ HS_EXPORT int hs_delta_recurrence(float* o, float* state, const float* qn, const
   int KS = 1;
   while (KS * hs::DR_DP < D) KS <<= 1;
   const int cols = hs::DR_THREADS / KS;
+  const int CH = KS * hs::DR_DP <= 128 ? 16 : 8;
+  const size_t smem = (size_t)(3 * CH * KS * hs::DR_DP + CH * cols + CH) * sizeof(float);
   dim3 grid(n_requests, heads, (V + cols - 1) / cols);
-  hs::delta_recurrence_kernel<<<grid, hs::DR_THREADS, 0, (cudaStream_t)stream>>>(
-      o, state, qn, kn, vv, beta, decay, req_start, req_len, req_slot, s, KS);
+  hs::delta_recurrence_kernel<<<grid, hs::DR_THREADS, smem, (cudaStream_t)stream>>>(
+      o, state, qn, kn, vv, beta, decay, req_start, req_len, req_slot, s, KS, CH);
   HS_LAUNCH_CHECK();
   return HS_OK;
 }

@@ -7,7 +7,9 @@
 //   out_lat[h]  = sum_j weight_j * c_j                        (R numbers; W_uv[h] follows)
 //
 // The sink of a head is a learned logit without key or value: it only enters the denominator.
-// Scores, the running maximum, the denominator and the accumulator are float32.
+// Scores, the running maximum, the denominator and the accumulator are float32.  A step of few
+// tokens splits each token's keys over several blocks whose shares (maximum, sum, weighted rows)
+// a second kernel merges; the split depends on the number of tokens in the step only.
 //
 // Pool rows: [pages, page_size, R + P] in the cache type; row of position p of request r is
 // table[r, p / page_size] * page_size + p % page_size.
@@ -65,7 +67,8 @@ latent_attention_kernel(float* __restrict__ out, const float* __restrict__ qa,
                         const int* __restrict__ table, const int* __restrict__ tok_pos,
                         const int* __restrict__ tok_req, const float* __restrict__ sink,
                         int n_heads, int R, int P, int qr_stride, int qr_hstride, int qr_off,
-                        float scale, int page_size, int num_pages, int max_pages, int* status) {
+                        float scale, int page_size, int num_pages, int max_pages, int* status,
+                        int nsplit, float* __restrict__ partial) {
   extern __shared__ float smem[];
   const int W = R + P;
   const int ks = W | 1;                         // odd row stride: lanes on rows hit distinct banks
@@ -88,13 +91,18 @@ latent_attention_kernel(float* __restrict__ out, const float* __restrict__ qa,
                 : qr[(size_t)t * qr_stride + (size_t)head * qr_hstride + qr_off + (d - R)];
     s_q[i] = v;
   }
-  float m = live ? sink[h] : 0.f;               // the sink opens the running softmax: weight 1
-  float l = 1.f;
+  // alone, a block opens its running softmax with the sink (weight 1); as one of `nsplit`
+  // blocks over the keys it starts empty and the sink joins when the shares are merged
+  float m = nsplit > 1 ? -INFINITY : (live ? sink[h] : 0.f);
+  float l = nsplit > 1 ? 0.f : 1.f;
   float acc[RC];
 #pragma unroll
   for (int i = 0; i < RC; ++i) acc[i] = 0.f;
   const float* q = s_q + warp * W;
-  for (int base = 0; base <= pos; base += LA_TILE) {
+  const int n_tiles = pos / LA_TILE + 1;
+  const int per = (n_tiles + nsplit - 1) / nsplit;
+  const int tile_lo = blockIdx.z * per, tile_hi = min(n_tiles, tile_lo + per);
+  for (int base = tile_lo * LA_TILE; base < tile_hi * LA_TILE; base += LA_TILE) {
     __syncthreads();                            // the tile before has been used (and s_q is set)
     const int nk = min(LA_TILE, pos + 1 - base);
     for (int j = warp; j < nk; j += LA_HB) {
@@ -137,12 +145,48 @@ latent_attention_kernel(float* __restrict__ out, const float* __restrict__ qa,
     }
   }
   if (!live) return;
+  if (nsplit > 1) {                             // this block's share: maximum, sum, weighted rows
+    float* ps = partial + (((size_t)t * n_heads + h) * nsplit + blockIdx.z) * (R + 2);
+    if (lane == 0) { ps[0] = m; ps[1] = l; }
+#pragma unroll
+    for (int i = 0; i < RC; ++i) {
+      const int d = lane + 32 * i;
+      if (d < R) ps[2 + d] = acc[i];
+    }
+    return;
+  }
   const float inv = 1.0f / l;
   float* o = out + ((size_t)t * n_heads + h) * R;
 #pragma unroll
   for (int i = 0; i < RC; ++i) {
     const int d = lane + 32 * i;
     if (d < R) o[d] = acc[i] * inv;
+  }
+}
+
+// Merges the shares of the blocks that split a token's keys, and lets the sink in (once).
+__global__ void latent_merge_kernel(float* __restrict__ out, const float* __restrict__ partial,
+                                    const float* __restrict__ sink,
+                                    const int* __restrict__ tok_req, int n_heads, int R,
+                                    int nsplit) {
+  const int t = blockIdx.x, h = blockIdx.y;
+  if (tok_req[t] < 0) return;
+  const float* ps = partial + ((size_t)t * n_heads + h) * nsplit * (R + 2);
+  float m = sink[h];
+  for (int s = 0; s < nsplit; ++s) m = fmaxf(m, ps[(size_t)s * (R + 2)]);
+  float l = expf(sink[h] - m);
+  for (int s = 0; s < nsplit; ++s) {
+    const float ms = ps[(size_t)s * (R + 2)];
+    if (ms > -INFINITY) l += ps[(size_t)s * (R + 2) + 1] * expf(ms - m);
+  }
+  const float inv = 1.0f / l;
+  for (int d = threadIdx.x; d < R; d += blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+      const float ms = ps[(size_t)s * (R + 2)];
+      if (ms > -INFINITY) a = fmaf(ps[(size_t)s * (R + 2) + 2 + d], expf(ms - m), a);
+    }
+    out[((size_t)t * n_heads + h) * R + d] = a * inv;
   }
 }
 
@@ -178,18 +222,24 @@ static int launch_latent_attention(float* out, const float* qa, const float* qr,
                                    const float* sink, int n_tokens, int n_heads, int R, int P,
                                    int qr_stride, int qr_hstride, int qr_off, float scale,
                                    int page_size, int num_pages, int max_pages, int* status,
-                                   cudaStream_t st) {
+                                   int nsplit, float* partial, cudaStream_t st) {
   const int W = R + P;
   const size_t smem = ((size_t)hs::LA_HB * W + (size_t)hs::LA_TILE * (W | 1)) * sizeof(float);
   if (smem > 200 * 1024) return HS_ERR_UNSUPPORTED;
   auto kern = hs::latent_attention_kernel<TC, RC>;
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  dim3 grid(n_tokens, (n_heads + hs::LA_HB - 1) / hs::LA_HB);
+  dim3 grid(n_tokens, (n_heads + hs::LA_HB - 1) / hs::LA_HB, nsplit);
   kern<<<grid, hs::LA_HB * 32, smem, st>>>(out, qa, qr, (const TC*)pool, table, tok_pos, tok_req,
                                            sink, n_heads, R, P, qr_stride, qr_hstride, qr_off,
-                                           scale, page_size, num_pages, max_pages, status);
+                                           scale, page_size, num_pages, max_pages, status, nsplit,
+                                           partial);
   HS_LAUNCH_CHECK();
+  if (nsplit > 1) {
+    hs::latent_merge_kernel<<<dim3(n_tokens, n_heads), 128, 0, st>>>(out, partial, sink, tok_req,
+                                                                     n_heads, R, nsplit);
+    HS_LAUNCH_CHECK();
+  }
   return HS_OK;
 }
 
@@ -198,7 +248,8 @@ HS_EXPORT int hs_latent_attention(float* out, const float* qa, const float* qr, 
                                   const float* sink, int n_tokens, int n_heads, int R, int P,
                                   int qr_stride, int qr_hstride, int qr_off, float scale,
                                   int page_size, int num_pages, int max_pages, int cache_dtype,
-                                  int* status, void* stream) {
+                                  int* status, int nsplit, float* partial, void* stream) {
+  if (nsplit < 1 || (nsplit > 1 && !partial)) return HS_ERR_ARGUMENT;
   if (!out || !qa || !qr || !pool || !table || !tok_pos || !tok_req || !sink || !status)
     return HS_ERR_ARGUMENT;
   if (R <= 0 || R > 512 || P < 0 || n_heads <= 0 || page_size <= 0) return HS_ERR_UNSUPPORTED;
@@ -209,7 +260,7 @@ HS_EXPORT int hs_latent_attention(float* out, const float* qa, const float* qr, 
   return launch_latent_attention<TC, RC>(out, qa, qr, pool, table, tok_pos, tok_req, sink,    \
                                          n_tokens, n_heads, R, P, qr_stride, qr_hstride,      \
                                          qr_off, scale, page_size, num_pages, max_pages,      \
-                                         status, st)
+                                         status, nsplit, partial, st)
 #define HS_LA_RC(TC)                   \
   do {                                 \
     if (rc <= 2) HS_LA(TC, 2);         \

@@ -1,21 +1,23 @@
-// Routed feed-forward (mixture of experts) on the CUDA cores.
+// Routed feed-forward (mixture of experts).
 //
 // route    per token: z = W_r h in float32, s = sigmoid(z).  Experts form `n_groups` equal groups
 //          of neighbours; a group's score is the sum of its two largest s; only experts of the
 //          `keep` best groups are eligible; the `top` eligible experts with the largest s are
 //          chosen (the lower index wins a tie) with weights s / (sum of the chosen s + 1e-20).
-// gate_up  per (token, chosen expert): g = min(W_g h, limit), u = clamp(W_u h, -limit, limit),
-//          y = g * sigmoid(1.702 g) * (u + 1)
-// down     per token: x += sum_k weight_k * (W_d[e_k] y_k), experts in the order they were chosen
+// expert   g = min(W_g h, limit), u = clamp(W_u h, -limit, limit), y = g * sigmoid(1.702 g) * (u + 1)
+// layer    x += sum_k weight_k * (W_d[e_k] y_k), experts in the order they were chosen
 //
-// Expert matrices are held k-major: gate/up [E, width, ff], down [E, ff, width], so that the
-// threads of a warp (one output each) read neighbouring weights.  Sums over k are sequential per
-// output in float32: a token's result does not depend on the batch around it.
+// Expert matrices are stacked as they are stored: gate / up [E, ff, width], down [E, width, ff]
+// (the summed index runs fastest).  Two paths:
+//   * few (token, expert) pairs, and all of float32: every pair streams its expert's rows, one
+//     warp per output row with 16-byte loads (a matrix-vector product per pair);
+//   * many pairs in bfloat16: the pairs are sorted by expert on the device (no host round
+//     trip), and tiles of 64 pairs x 64 outputs of one expert go through mma.sync m16n8k16 with
+//     float32 accumulators; the down projection's rows are added into the stream per token in
+//     the order the experts were chosen, so a token's result does not depend on its neighbours.
 #include "common.cuh"
 
 namespace hs {
-
-constexpr int MOE_ROUTE_WARPS = 4;
 
 // (value, index) argmax over a warp; larger value wins, then the lower index
 __device__ __forceinline__ void warp_argmax(float& v, int& i) {
@@ -27,26 +29,32 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
   }
 }
 
+constexpr int ROUTE_THREADS = 128;
+
+// One block per token: the warps share the experts' dot products, warp 0 then chooses.
 template <typename TH>
-__global__ void __launch_bounds__(MOE_ROUTE_WARPS * 32)
+__global__ void __launch_bounds__(ROUTE_THREADS)
 moe_route_kernel(int* __restrict__ sel_idx, float* __restrict__ sel_w, const TH* __restrict__ h,
-                 const float* __restrict__ w_router, const int* __restrict__ tok_req,
-                 int n_tokens, int width, int E, int top, int n_groups, int keep) {
+                 const float* __restrict__ w_router, const int* __restrict__ tok_req, int width,
+                 int E, int top, int n_groups, int keep) {
   extern __shared__ float smem[];
+  float* s_h = smem;                // [width]
+  float* s_s = smem + width;        // [E] scores (-1 once taken)
+  float* s_g = s_s + E;             // [n_groups] (-2 marks a kept group)
+  const int t = blockIdx.x;
+  if (tok_req[t] < 0) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * MOE_ROUTE_WARPS + warp;
-  if (t >= n_tokens || tok_req[t] < 0) return;        // a warp works alone: no block barrier below
-  float* s_s = smem + (size_t)warp * (E + n_groups);  // [E] scores (then -1 when taken / barred)
-  float* s_g = s_s + E;                               // [n_groups]
-  const TH* hr = h + (size_t)t * width;
-  for (int e = 0; e < E; ++e) {
+  for (int k = threadIdx.x; k < width; k += ROUTE_THREADS) s_h[k] = to_f(h[(size_t)t * width + k]);
+  __syncthreads();
+  for (int e = warp; e < E; e += ROUTE_THREADS / 32) {
     const float* wr = w_router + (size_t)e * width;
     float z = 0.f;
-    for (int k = lane; k < width; k += 32) z = fmaf(wr[k], to_f(hr[k]), z);
+    for (int k = lane; k < width; k += 32) z = fmaf(wr[k], s_h[k], z);
     z = warp_sum(z);
     if (lane == 0) s_s[e] = 1.0f / (1.0f + expf(-z));
   }
-  __syncwarp();
+  __syncthreads();
+  if (warp != 0) return;
   const int per = E / n_groups;
   for (int g = lane; g < n_groups; g += 32) {
     float a = -1.f, b = -1.f;                          // the two largest of the group
@@ -57,7 +65,6 @@ moe_route_kernel(int* __restrict__ sel_idx, float* __restrict__ sel_w, const TH*
     s_g[g] = per > 1 ? a + b : a;
   }
   __syncwarp();
-  // the `keep` best groups stay; the others are barred.  A kept group is marked by score -2.
   for (int round = 0; round < keep; ++round) {
     float bv = -1.f;
     int bi = 0x7fffffff;
@@ -67,7 +74,6 @@ moe_route_kernel(int* __restrict__ sel_idx, float* __restrict__ sel_w, const TH*
     if (lane == 0) s_g[bi] = -2.f;
     __syncwarp();
   }
-  // choose: `top` rounds of argmax over eligible experts
   float chosen_v = 0.f;                                // lane k keeps the k-th choice (top <= 32)
   int chosen_i = 0;
   float total = 0.f;
@@ -90,60 +96,295 @@ moe_route_kernel(int* __restrict__ sel_idx, float* __restrict__ sel_w, const TH*
   }
 }
 
-constexpr int MOE_THREADS = 128;
+__device__ __forceinline__ float expert_act(float g, float u, float limit) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g * (1.0f / (1.0f + expf(-1.702f * g))) * (u + 1.0f);
+}
+
+// -- path 1: a matrix-vector product per pair ---------------------------------------------------
+// dot of a weight row (n contiguous values) with a float32 vector in shared memory, over a warp
+__device__ __forceinline__ float row_dot(const float* __restrict__ w, const float* v, int n,
+                                         int lane) {
+  float acc = 0.f;
+  if ((n & 3) == 0 && (((uintptr_t)w) & 15) == 0) {
+    for (int k = lane * 4; k < n; k += 128) {
+      const float4 a = *(const float4*)(w + k);
+      acc = fmaf(a.x, v[k], acc); acc = fmaf(a.y, v[k + 1], acc);
+      acc = fmaf(a.z, v[k + 2], acc); acc = fmaf(a.w, v[k + 3], acc);
+    }
+  } else {
+    for (int k = lane; k < n; k += 32) acc = fmaf(w[k], v[k], acc);
+  }
+  return warp_sum(acc);
+}
+__device__ __forceinline__ float row_dot(const __nv_bfloat16* __restrict__ w, const float* v,
+                                         int n, int lane) {
+  float acc = 0.f;
+  if ((n & 7) == 0 && (((uintptr_t)w) & 15) == 0) {
+    for (int k = lane * 8; k < n; k += 256) {
+      const uint4 raw = *(const uint4*)(w + k);
+      const __nv_bfloat162* p = (const __nv_bfloat162*)&raw;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(p[i]);
+        acc = fmaf(f.x, v[k + 2 * i], acc);
+        acc = fmaf(f.y, v[k + 2 * i + 1], acc);
+      }
+    }
+  } else {
+    for (int k = lane; k < n; k += 32) acc = fmaf(__bfloat162float(w[k]), v[k], acc);
+  }
+  return warp_sum(acc);
+}
+
+constexpr int GEMV_THREADS = 256;
+constexpr int GEMV_ROWS = 32;       // output rows a block covers
 
 template <typename TW>
-__global__ void __launch_bounds__(MOE_THREADS)
-moe_gate_up_kernel(float* __restrict__ y, const TW* __restrict__ h, const TW* __restrict__ w_gate,
-                   const TW* __restrict__ w_up, const int* __restrict__ sel_idx,
-                   const int* __restrict__ tok_req, int width, int ff, int top, int E,
-                   float limit) {
+__global__ void __launch_bounds__(GEMV_THREADS)
+moe_gate_up_rows_kernel(float* __restrict__ y, const TW* __restrict__ h,
+                        const TW* __restrict__ w_gate, const TW* __restrict__ w_up,
+                        const int* __restrict__ sel_idx, const int* __restrict__ tok_req,
+                        int width, int ff, int top, int E, float limit) {
   extern __shared__ float s_h[];                       // [width]
   const int pair = blockIdx.x;
   const int t = pair / top;
   if (tok_req[t] < 0) return;
   const int e = sel_idx[pair];
   if (e < 0 || e >= E) return;
-  for (int k = threadIdx.x; k < width; k += MOE_THREADS) s_h[k] = to_f(h[(size_t)t * width + k]);
+  for (int k = threadIdx.x; k < width; k += GEMV_THREADS) s_h[k] = to_f(h[(size_t)t * width + k]);
   __syncthreads();
-  const int f = blockIdx.y * MOE_THREADS + threadIdx.x;
-  if (f >= ff) return;
-  const TW* wg = w_gate + (size_t)e * width * ff + f;
-  const TW* wu = w_up + (size_t)e * width * ff + f;
-  float g = 0.f, u = 0.f;
-  for (int k = 0; k < width; ++k) {
-    const float hv = s_h[k];
-    g = fmaf(to_f(wg[(size_t)k * ff]), hv, g);
-    u = fmaf(to_f(wu[(size_t)k * ff]), hv, u);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int f_end = min(ff, (int)(blockIdx.y + 1) * GEMV_ROWS);
+  for (int f = blockIdx.y * GEMV_ROWS + warp; f < f_end; f += GEMV_THREADS / 32) {
+    const size_t row = ((size_t)e * ff + f) * width;
+    const float g = row_dot(w_gate + row, s_h, width, lane);
+    const float u = row_dot(w_up + row, s_h, width, lane);
+    if (lane == 0) y[(size_t)pair * ff + f] = expert_act(g, u, limit);
   }
-  g = fminf(g, limit);
-  u = fminf(fmaxf(u, -limit), limit);
-  y[(size_t)pair * ff + f] = g * (1.0f / (1.0f + expf(-1.702f * g))) * (u + 1.0f);
 }
 
 template <typename TW>
-__global__ void __launch_bounds__(MOE_THREADS)
-moe_down_kernel(float* __restrict__ x, const float* __restrict__ y, const TW* __restrict__ w_down,
-                const int* __restrict__ sel_idx, const float* __restrict__ sel_w,
-                const int* __restrict__ tok_req, int width, int ff, int top, int E) {
+__global__ void __launch_bounds__(GEMV_THREADS)
+moe_down_rows_kernel(float* __restrict__ x, const float* __restrict__ y,
+                     const TW* __restrict__ w_down, const int* __restrict__ sel_idx,
+                     const float* __restrict__ sel_w, const int* __restrict__ tok_req, int width,
+                     int ff, int top, int E) {
   extern __shared__ float s_y[];                       // [top][ff]
   const int t = blockIdx.x;
   if (tok_req[t] < 0) return;
-  for (int i = threadIdx.x; i < top * ff; i += MOE_THREADS) s_y[i] = y[(size_t)t * top * ff + i];
+  for (int i = threadIdx.x; i < top * ff; i += GEMV_THREADS) s_y[i] = y[(size_t)t * top * ff + i];
   __syncthreads();
-  const int n = blockIdx.y * MOE_THREADS + threadIdx.x;
-  if (n >= width) return;
-  float sum = 0.f;
-  for (int k = 0; k < top; ++k) {
-    const int e = sel_idx[(size_t)t * top + k];
-    if (e < 0 || e >= E) continue;
-    const TW* wd = w_down + (size_t)e * ff * width + n;
-    const float* yk = s_y + (size_t)k * ff;
-    float acc = 0.f;
-    for (int f = 0; f < ff; ++f) acc = fmaf(to_f(wd[(size_t)f * width]), yk[f], acc);
-    sum = fmaf(sel_w[(size_t)t * top + k], acc, sum);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_end = min(width, (int)(blockIdx.y + 1) * GEMV_ROWS);
+  for (int n = blockIdx.y * GEMV_ROWS + warp; n < n_end; n += GEMV_THREADS / 32) {
+    float sum = 0.f;
+    for (int k = 0; k < top; ++k) {
+      const int e = sel_idx[(size_t)t * top + k];
+      if (e < 0 || e >= E) continue;
+      const float acc = row_dot(w_down + ((size_t)e * width + n) * ff, s_y + (size_t)k * ff, ff, lane);
+      sum = fmaf(sel_w[(size_t)t * top + k], acc, sum);
+    }
+    if (lane == 0) x[(size_t)t * width + n] += sum;
   }
-  x[(size_t)t * width + n] += sum;
+}
+
+// -- path 2: pairs sorted by expert, tiles on the tensor cores --------------------------------
+constexpr int TM = 64, TN = 64, TK = 32;     // tile of pairs x outputs, step over the summed index
+constexpr int TS = TK + 8;                   // shared row stride in elements (80 bytes)
+constexpr int SORT_THREADS = 1024;
+
+// work: [0] number of tiles; then per expert E counts, E segment starts; then per tile its
+// expert and its first row.  pair_pos[pair] = row of the pair in expert order (-1: not there),
+// row_token[row] = the token of that row.
+__global__ void __launch_bounds__(SORT_THREADS)
+moe_sort_kernel(int* __restrict__ work, int* __restrict__ pair_pos, int* __restrict__ row_token,
+                const int* __restrict__ sel_idx, const int* __restrict__ tok_req, int n_tokens,
+                int top, int E, int max_tiles) {
+  extern __shared__ int s_cnt[];             // [E] counts, then [E] cursors
+  int* s_cur = s_cnt + E;
+  for (int e = threadIdx.x; e < E; e += SORT_THREADS) s_cnt[e] = 0;
+  __syncthreads();
+  const int pairs = n_tokens * top;
+  for (int p = threadIdx.x; p < pairs; p += SORT_THREADS) {
+    const int e = sel_idx[p];
+    if (tok_req[p / top] >= 0 && e >= 0 && e < E) atomicAdd(&s_cnt[e], 1);
+  }
+  __syncthreads();
+  int* counts = work + 1;
+  int* starts = work + 1 + E;
+  int* tile_e = work + 1 + 2 * E;
+  int* tile_r = tile_e + max_tiles;
+  if (threadIdx.x == 0) {
+    int at = 0, tiles = 0;
+    for (int e = 0; e < E; ++e) {
+      counts[e] = s_cnt[e];
+      starts[e] = at;
+      s_cur[e] = at;
+      for (int r = 0; r < s_cnt[e] && tiles < max_tiles; r += TM) {
+        tile_e[tiles] = e;
+        tile_r[tiles] = at + r;
+        ++tiles;
+      }
+      at += s_cnt[e];
+    }
+    work[0] = tiles;
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += SORT_THREADS) {
+    const int e = sel_idx[p];
+    int pos = -1;
+    if (tok_req[p / top] >= 0 && e >= 0 && e < E) {
+      pos = atomicAdd(&s_cur[e], 1);
+      row_token[pos] = p / top;
+    }
+    pair_pos[p] = pos;
+  }
+}
+
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, const uint32_t* b) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+// Loads a [64 rows x 32] bfloat16 tile into registers: thread i takes 16-byte pieces i and
+// i + 128 (piece c: row c / 4, columns 8 (c % 4) ..).  Rows at or beyond `rows` are zero.
+// `row_ptr(r)` gives the start of row r.
+template <typename RowPtr>
+__device__ __forceinline__ void tile_fetch(uint4* regs, RowPtr row_ptr, int rows, int k0) {
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int c = threadIdx.x + 128 * j;
+    const int r = c >> 2, col = (c & 3) * 8;
+    regs[j] = r < rows ? *(const uint4*)(row_ptr(r) + k0 + col) : make_uint4(0, 0, 0, 0);
+  }
+}
+__device__ __forceinline__ void tile_store(__nv_bfloat16* s, const uint4* regs) {
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int c = threadIdx.x + 128 * j;
+    *(uint4*)(s + (c >> 2) * TS + (c & 3) * 8) = regs[j];
+  }
+}
+
+// One block: 64 rows of one expert's segment x 64 outputs.  NB = 2: gate and up together with
+// the activation as epilogue (out: bfloat16 rows); NB = 1: the down projection (out: float32).
+// A rows: `a` indexed through row_token when GATHER (the normed rows of the tokens), else the
+// sorted rows themselves.  4 warps, each 32 x 32 of the tile.
+template <int NB, bool GATHER>
+__global__ void __launch_bounds__(128)
+moe_tiles_kernel(void* __restrict__ out, const __nv_bfloat16* __restrict__ a,
+                 const __nv_bfloat16* __restrict__ w0, const __nv_bfloat16* __restrict__ w1,
+                 const int* __restrict__ work, const int* __restrict__ row_token, int E,
+                 int max_tiles, int N, int K, float limit) {
+  __shared__ __align__(16) __nv_bfloat16 s_a[TM * TS];
+  __shared__ __align__(16) __nv_bfloat16 s_b[NB][TN * TS];
+  const int tile = blockIdx.x;
+  if (tile >= work[0]) return;
+  const int e = work[1 + 2 * E + tile];
+  const int row0 = work[1 + 2 * E + max_tiles + tile];
+  const int seg_end = work[1 + E + e] + work[1 + e];
+  const int rows = min(TM, seg_end - row0);
+  const int n0 = blockIdx.y * TN;
+  const int ncols = min(TN, N - n0);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
+  const int g = lane >> 2, tq = lane & 3;
+  auto a_row = [&](int r) {
+    const int src = GATHER ? row_token[row0 + r] : row0 + r;
+    return a + (size_t)src * K;
+  };
+  const __nv_bfloat16* b0 = w0 + ((size_t)e * N + n0) * K;
+  const __nv_bfloat16* b1 = NB == 2 ? w1 + ((size_t)e * N + n0) * K : nullptr;
+  auto b0_row = [&](int r) { return b0 + (size_t)r * K; };
+  auto b1_row = [&](int r) { return b1 + (size_t)r * K; };
+  float acc[NB][2][4][4];
+#pragma unroll
+  for (int x = 0; x < NB; ++x)
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[x][i][j][c] = 0.f;
+  uint4 ra[2], rb[NB][2];
+  tile_fetch(ra, a_row, rows, 0);
+  tile_fetch(rb[0], b0_row, ncols, 0);
+  if (NB == 2) tile_fetch(rb[NB - 1], b1_row, ncols, 0);
+  for (int k0 = 0; k0 < K; k0 += TK) {
+    __syncthreads();                              // the tile before has been used
+    tile_store(s_a, ra);
+    tile_store(s_b[0], rb[0]);
+    if (NB == 2) tile_store(s_b[NB - 1], rb[NB - 1]);
+    __syncthreads();
+    if (k0 + TK < K) {                            // the next tile travels while this one is used
+      tile_fetch(ra, a_row, rows, k0 + TK);
+      tile_fetch(rb[0], b0_row, ncols, k0 + TK);
+      if (NB == 2) tile_fetch(rb[NB - 1], b1_row, ncols, k0 + TK);
+    }
+#pragma unroll
+    for (int kk = 0; kk < TK; kk += 16) {
+      uint32_t fa[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const __nv_bfloat16* p = s_a + (wm + 16 * i + g) * TS + kk + 2 * tq;
+        fa[i][0] = *(const uint32_t*)p;
+        fa[i][1] = *(const uint32_t*)(p + 8 * TS);
+        fa[i][2] = *(const uint32_t*)(p + 8);
+        fa[i][3] = *(const uint32_t*)(p + 8 * TS + 8);
+      }
+#pragma unroll
+      for (int x = 0; x < NB; ++x)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const __nv_bfloat16* p = s_b[x] + (wn + 8 * j + g) * TS + kk + 2 * tq;
+          uint32_t fb[2] = {*(const uint32_t*)p, *(const uint32_t*)(p + 8)};
+#pragma unroll
+          for (int i = 0; i < 2; ++i) mma_bf16(acc[x][i][j], fa[i], fb);
+        }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int r = wm + 16 * i + g + 8 * half;
+        const int c = wn + 8 * j + 2 * tq;
+        if (r >= rows) continue;
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          if (c + q >= ncols) continue;
+          const size_t at = (size_t)(row0 + r) * N + n0 + c + q;
+          if (NB == 2)
+            ((__nv_bfloat16*)out)[at] = __float2bfloat16_rn(
+                expert_act(acc[0][i][j][2 * half + q], acc[NB - 1][i][j][2 * half + q], limit));
+          else
+            ((float*)out)[at] = acc[0][i][j][2 * half + q];
+        }
+      }
+}
+
+// x[t] += sum_k weight_k * rows[pair_pos[t, k]], experts in the order they were chosen
+__global__ void moe_combine_kernel(float* __restrict__ x, const float* __restrict__ rows,
+                                   const int* __restrict__ pair_pos,
+                                   const float* __restrict__ sel_w,
+                                   const int* __restrict__ tok_req, int width, int top) {
+  const int t = blockIdx.x;
+  if (tok_req[t] < 0) return;
+  for (int n = threadIdx.x; n < width; n += blockDim.x) {
+    float sum = 0.f;
+    for (int k = 0; k < top; ++k) {
+      const int pos = pair_pos[(size_t)t * top + k];
+      if (pos >= 0) sum = fmaf(sel_w[(size_t)t * top + k], rows[(size_t)pos * width + n], sum);
+    }
+    x[(size_t)t * width + n] += sum;
+  }
 }
 
 }  // namespace hs
@@ -156,52 +397,98 @@ HS_EXPORT int hs_moe_route(int* sel_idx, float* sel_w, const void* h, const floa
       keep > n_groups || top > keep * (E / n_groups))
     return HS_ERR_UNSUPPORTED;
   if (n_tokens <= 0) return HS_OK;
-  const size_t smem = (size_t)hs::MOE_ROUTE_WARPS * (E + n_groups) * sizeof(float);
+  const size_t smem = (size_t)(width + E + n_groups) * sizeof(float);
   if (smem > 48 * 1024) return HS_ERR_UNSUPPORTED;
-  const int grid = (n_tokens + hs::MOE_ROUTE_WARPS - 1) / hs::MOE_ROUTE_WARPS;
   cudaStream_t st = (cudaStream_t)stream;
   if (h_dtype == HS_DT_F32)
-    hs::moe_route_kernel<float><<<grid, hs::MOE_ROUTE_WARPS * 32, smem, st>>>(
-        sel_idx, sel_w, (const float*)h, w_router, tok_req, n_tokens, width, E, top, n_groups,
-        keep);
+    hs::moe_route_kernel<float><<<n_tokens, hs::ROUTE_THREADS, smem, st>>>(
+        sel_idx, sel_w, (const float*)h, w_router, tok_req, width, E, top, n_groups, keep);
   else if (h_dtype == HS_DT_BF16)
-    hs::moe_route_kernel<__nv_bfloat16><<<grid, hs::MOE_ROUTE_WARPS * 32, smem, st>>>(
-        sel_idx, sel_w, (const __nv_bfloat16*)h, w_router, tok_req, n_tokens, width, E, top,
-        n_groups, keep);
+    hs::moe_route_kernel<__nv_bfloat16><<<n_tokens, hs::ROUTE_THREADS, smem, st>>>(
+        sel_idx, sel_w, (const __nv_bfloat16*)h, w_router, tok_req, width, E, top, n_groups,
+        keep);
   else
     return HS_ERR_UNSUPPORTED;
   HS_LAUNCH_CHECK();
   return HS_OK;
 }
 
+// Scratch of the sorted path for n_tokens x top pairs: ints (work lists, pair positions, row
+// tokens) and bytes of rows (bfloat16 activations, then float32 outputs of the down projection).
+// Returns 0 and zeros when the sorted path does not take the shape.
+HS_EXPORT int hs_moe_sorted_scratch(int n_tokens, int width, int ff, int top, int E, int dtype,
+                                    long long* ints, long long* bytes) {
+  *ints = 0;
+  *bytes = 0;
+  const long long pairs = (long long)n_tokens * top;
+  if (dtype != HS_DT_BF16 || width % hs::TK || ff % hs::TK || pairs < 256 || E > 4096)
+    return HS_OK;
+  const long long max_tiles = pairs / hs::TM + E;
+  *ints = 1 + 2LL * E + 2 * max_tiles + 2 * pairs;
+  *bytes = ((pairs * ff * 2 + 255) / 256) * 256 + pairs * width * 4;
+  return HS_OK;
+}
+
+// `y`: float32 scratch [pairs, ff] of the row path.  `ints` / `rows`: scratch of the sorted path
+// (sized by hs_moe_sorted_scratch; null to use the row path).
 HS_EXPORT int hs_moe_experts(float* x, float* y, const void* h, const void* w_gate,
                              const void* w_up, const void* w_down, const int* sel_idx,
                              const float* sel_w, const int* tok_req, int n_tokens, int width,
-                             int ff, int top, int E, float limit, int dtype, void* stream) {
-  if (!x || !y || !h || !w_gate || !w_up || !w_down || !sel_idx || !sel_w || !tok_req)
+                             int ff, int top, int E, float limit, int dtype, int* ints,
+                             void* rows, void* stream) {
+  if (!x || !h || !w_gate || !w_up || !w_down || !sel_idx || !sel_w || !tok_req)
     return HS_ERR_ARGUMENT;
   if (width <= 0 || ff <= 0 || top <= 0 || E <= 0) return HS_ERR_UNSUPPORTED;
   if (n_tokens <= 0) return HS_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (ints && rows) {
+    long long need_i = 0, need_b = 0;
+    hs_moe_sorted_scratch(n_tokens, width, ff, top, E, dtype, &need_i, &need_b);
+    if (need_i == 0) return HS_ERR_UNSUPPORTED;
+    const int pairs = n_tokens * top;
+    const int max_tiles = pairs / hs::TM + E;
+    int* work = ints;
+    int* pair_pos = ints + 1 + 2 * E + 2 * max_tiles;
+    int* row_token = pair_pos + pairs;
+    __nv_bfloat16* act = (__nv_bfloat16*)rows;
+    float* down = (float*)((char*)rows + (((size_t)pairs * ff * 2 + 255) / 256) * 256);
+    hs::moe_sort_kernel<<<1, hs::SORT_THREADS, 2 * E * sizeof(int), st>>>(
+        work, pair_pos, row_token, sel_idx, tok_req, n_tokens, top, E, max_tiles);
+    HS_LAUNCH_CHECK();
+    const __nv_bfloat16* hb = (const __nv_bfloat16*)h;
+    hs::moe_tiles_kernel<2, true><<<dim3(max_tiles, (ff + hs::TN - 1) / hs::TN), 128, 0, st>>>(
+        act, hb, (const __nv_bfloat16*)w_gate, (const __nv_bfloat16*)w_up, work, row_token, E,
+        max_tiles, ff, width, limit);
+    HS_LAUNCH_CHECK();
+    hs::moe_tiles_kernel<1, false><<<dim3(max_tiles, (width + hs::TN - 1) / hs::TN), 128, 0, st>>>(
+        down, act, (const __nv_bfloat16*)w_down, nullptr, work, row_token, E, max_tiles, width,
+        ff, limit);
+    HS_LAUNCH_CHECK();
+    hs::moe_combine_kernel<<<n_tokens, 256, 0, st>>>(x, down, pair_pos, sel_w, tok_req, width,
+                                                     top);
+    HS_LAUNCH_CHECK();
+    return HS_OK;
+  }
+  if (!y) return HS_ERR_ARGUMENT;
   const size_t smem_h = (size_t)width * sizeof(float);
   const size_t smem_y = (size_t)top * ff * sizeof(float);
   if (smem_h > 200 * 1024 || smem_y > 200 * 1024) return HS_ERR_UNSUPPORTED;
-  cudaStream_t st = (cudaStream_t)stream;
-  dim3 g1(n_tokens * top, (ff + hs::MOE_THREADS - 1) / hs::MOE_THREADS);
-  dim3 g2(n_tokens, (width + hs::MOE_THREADS - 1) / hs::MOE_THREADS);
+  dim3 g1(n_tokens * top, (ff + hs::GEMV_ROWS - 1) / hs::GEMV_ROWS);
+  dim3 g2(n_tokens, (width + hs::GEMV_ROWS - 1) / hs::GEMV_ROWS);
 #define HS_MOE(TW)                                                                             \
   do {                                                                                         \
-    auto k1 = hs::moe_gate_up_kernel<TW>;                                                      \
-    auto k2 = hs::moe_down_kernel<TW>;                                                         \
+    auto k1 = hs::moe_gate_up_rows_kernel<TW>;                                                 \
+    auto k2 = hs::moe_down_rows_kernel<TW>;                                                    \
     if (smem_h > 48 * 1024)                                                                    \
       cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_h);      \
     if (smem_y > 48 * 1024)                                                                    \
       cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_y);      \
-    k1<<<g1, hs::MOE_THREADS, smem_h, st>>>(y, (const TW*)h, (const TW*)w_gate,                \
-                                            (const TW*)w_up, sel_idx, tok_req, width, ff, top, \
-                                            E, limit);                                         \
+    k1<<<g1, hs::GEMV_THREADS, smem_h, st>>>(y, (const TW*)h, (const TW*)w_gate,               \
+                                             (const TW*)w_up, sel_idx, tok_req, width, ff,     \
+                                             top, E, limit);                                   \
     HS_LAUNCH_CHECK();                                                                         \
-    k2<<<g2, hs::MOE_THREADS, smem_y, st>>>(x, y, (const TW*)w_down, sel_idx, sel_w, tok_req,  \
-                                            width, ff, top, E);                                \
+    k2<<<g2, hs::GEMV_THREADS, smem_y, st>>>(x, y, (const TW*)w_down, sel_idx, sel_w, tok_req, \
+                                             width, ff, top, E);                               \
   } while (0)
   if (dtype == HS_DT_F32) HS_MOE(float);
   else if (dtype == HS_DT_BF16) HS_MOE(__nv_bfloat16);

@@ -188,12 +188,14 @@ def _declare(lib) -> None:
         "hs_rotary_pairs": [P, P, P, P, I, I, I, I, I, I, P],
         "hs_grouped_linear": [P, P, P, I, I, I, I, I, I, I, I, I, P],
         "hs_latent_append": [P, P, P, P, P, P, I, I, I, I, I, F, I, I, I, I, P, P],
-        "hs_latent_attention": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, I, I, P, P],
+        "hs_latent_attention": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, I, I, P, I,
+                                P, P],
         "hs_delta_prepare": [P] * 15 + [I] * 9 + [P],
         "hs_delta_recurrence": [P] * 10 + [I] * 8 + [P],
         "hs_delta_finish": [P, P, P, P, P, P, I, F, I, I, I, I, I, I, I, I, P],
         "hs_moe_route": [P, P, P, P, P, I, I, I, I, I, I, I, P],
-        "hs_moe_experts": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, F, I, P],
+        "hs_moe_experts": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, F, I, P, P, P],
+        "hs_moe_sorted_scratch": [I, I, I, I, I, I, P, P],
         "hs_sample": [P, P, P, P, P, P, P, I, I, P, P, P, P],
     }
     for name, argtypes in sig.items():
@@ -279,6 +281,11 @@ class CudaOps:
         self.fuse_append = True    # key/value append fused into the decode attention
         self.pdl = True            # programmatic dependent launch (see the property below)
         self._skinny_need: dict = {}
+        self._moe_need: dict = {}
+        self.latent_splits = None   # blocks a token's keys are split over in latent attention
+        #                             (None: chosen from the number of tokens in the step)
+        self.sorted_experts = True  # many (token, expert) pairs in bfloat16: sorted by expert and
+        #                             run as tiles on the tensor cores (False: a product per pair)
         self._tc_need: dict = {}
         self._scratch: dict = {}
         self._retired: list = []
@@ -1043,12 +1050,22 @@ class CudaOps:
             raise KernelError("latent_attention: the rotated query parts exceed qr's row")
         if pool.numel() % (page_size * W) or sink.shape[0] != n_heads:
             raise KernelError("latent_attention: pool or sink does not fit")
-        self.launches += 1
+        # few tokens: the keys of each are split over several blocks so that the device fills
+        blocks = n * -(-n_heads // 8)
+        nsplit = 1 if blocks >= self.sm_count else min(16, -(-2 * self.sm_count // blocks))
+        if self.latent_splits is not None:
+            nsplit = int(self.latent_splits)
+        partial = None
+        if nsplit > 1:
+            partial = self._scratch_buffer("latent_partial", n * n_heads * nsplit * (rank + 2),
+                                           torch.float32)
+        self.launches += 2 if nsplit > 1 else 1
         _check(self.lib.hs_latent_attention(
             _ptr(out), _ptr(qa), _ptr(qr), _ptr(pool), _ptr(table), _ptr(tok_pos), _ptr(tok_req),
             _ptr(sink), n, n_heads, rank, rot_dim, qr.shape[1], int(qr_head_stride),
             int(qr_offset), float(scale), page_size, pool.numel() // (page_size * W),
-            table.shape[1], _DT[pool.dtype], _ptr(status), self._stream()),
+            table.shape[1], _DT[pool.dtype], _ptr(status), nsplit, _ptr(partial),
+            self._stream()),
             f"latent_attention(rank={rank},rot_dim={rot_dim})")
 
     # -- the gated delta rule ---------------------------------------------------------------
@@ -1098,7 +1115,8 @@ class CudaOps:
             taps, ra, rg, self._stream()), f"delta_recurrence(dim={D},vdim={V})")
 
     def delta_finish(self, out, o, proj, g2, norm_w, tok_req, eps, shape):
-        """out = o / sqrt(mean(o^2) + eps) per head * norm_w * sigmoid(g2 g)."""
+        """out = o / sqrt(mean(o^2) + eps) per head * norm_w * sigmoid(g2^T g); ``g2`` is
+        [g_rank, heads * vdim] (and ``a2`` of :meth:`delta_prepare` [a_rank, heads * dim])."""
         H, HK, D, V, taps, ra, rg = self._delta_sizes(shape)
         _want(out, "out", _FLOATS, 2)
         _want(o, "o", torch.float32, 2)
@@ -1131,24 +1149,39 @@ class CudaOps:
     def moe_experts(self, x, y, h, w_gate, w_up, w_down, sel_idx, sel_w, tok_req, *, limit):
         """x += sum over a token's chosen experts of weight * W_down act(W_gate h, W_up h) with
         act(g, u) = min(g, limit) * sigmoid(1.702 min(g, limit)) * (clamp(u, +-limit) + 1).
-        Expert matrices k-major: gate / up [E, width, ff], down [E, ff, width]; ``y`` is
-        float32 scratch [T * top, ff]."""
+        Expert matrices stacked as stored: gate / up [E, ff, width], down [E, width, ff]; ``y``
+        is float32 scratch [T * top, ff].  Many pairs in bfloat16 are sorted by expert on the
+        device and run as tiles on the tensor cores; few pairs, and float32, as one
+        matrix-vector product per pair."""
         _want(x, "x", torch.float32, 2)
         _want(y, "y", torch.float32, 2)
         _want(h, "h", _FLOATS, 2)
         for t, nm in ((w_gate, "w_gate"), (w_up, "w_up"), (w_down, "w_down")):
             _want(t, nm, h.dtype, 3)
-        E, width, ff = w_gate.shape
+        E, ff, width = w_gate.shape
         T, top = sel_idx.shape
-        if tuple(w_up.shape) != (E, width, ff) or tuple(w_down.shape) != (E, ff, width) \
+        if tuple(w_up.shape) != (E, ff, width) or tuple(w_down.shape) != (E, width, ff) \
                 or h.shape[1] != width or x.shape[1] != width or y.shape[0] < T * top \
                 or y.shape[1] != ff:
             raise KernelError("moe_experts: shapes do not fit")
-        self.launches += 2
+        key = (T, width, ff, top, E, h.dtype)
+        need = self._moe_need.get(key)
+        if need is None:
+            ni, nb = ctypes.c_longlong(0), ctypes.c_longlong(0)
+            self.lib.hs_moe_sorted_scratch(T, width, ff, top, E, _DT[h.dtype], ctypes.byref(ni),
+                                           ctypes.byref(nb))
+            need = (ni.value, nb.value) if self.sorted_experts else (0, 0)
+            self._moe_need[key] = need
+        ints = rows = None
+        if need[0]:
+            ints = self._scratch_buffer("moe_ints", need[0], torch.int32)
+            rows = self._scratch_buffer("moe_rows", need[1], torch.uint8)
+        self.launches += 4 if ints is not None else 2
         _check(self.lib.hs_moe_experts(_ptr(x), _ptr(y), _ptr(h), _ptr(w_gate), _ptr(w_up),
                                        _ptr(w_down), _ptr(sel_idx), _ptr(sel_w), _ptr(tok_req),
                                        T, width, ff, top, E, float(limit), _DT[h.dtype],
-                                       self._stream()), f"moe_experts(ff={ff})")
+                                       _ptr(ints), _ptr(rows), self._stream()),
+               f"moe_experts(ff={ff})")
 
     # -- sampling ---------------------------------------------------------------
     def argmax(self, out, logits):

@@ -64,7 +64,8 @@ class ChannelDeltaRule(Mixer):
         self.w_in = torch.cat([t[p + "q"], t[p + "k"], t[p + "v"], t[p + "b"], t[p + "a1"],
                                t[p + "g1"]]).contiguous()
         self.conv_w = torch.cat([t[p + "q.conv"], t[p + "k.conv"], t[p + "v.conv"]]).contiguous()
-        self.a2, self.g2 = t[p + "a2"], t[p + "g2"]
+        # the kernels read these two with the summed index slowest
+        self.a2, self.g2 = t[p + "a2"].t().contiguous(), t[p + "g2"].t().contiguous()
         self.dt_bias, self.a_log, self.norm_w = t[p + "dt_bias"], t[p + "A_log"], t[p + "norm"]
         self.w_out = t[p + "o"]
         self.shape = dict(heads=self.H, kv_heads=self.HK, dim=self.D, vdim=self.V,

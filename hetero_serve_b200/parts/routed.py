@@ -9,7 +9,7 @@ Their weights are their scores divided by the scores' sum (+ 1e-20).  An expert 
     y = g * sigmoid(1.702 g) * (u + 1);   output W_down y
 
 and the layer adds the weighted sum of the chosen experts' outputs into the stream.  The
-experts' matrices are stacked once at binding, k-major, so that one kernel serves all experts.
+experts' matrices are stacked once at binding so that one kernel serves all experts.
 Routing happens on the device; cache and scheduler know nothing of it.
 """
 
@@ -45,8 +45,8 @@ class RoutedExperts(FeedForward):
     def bind(self, tensors):
         self.w_router = tensors[self.router_name]
 
-        def stack(which):          # [E, in, out]: the k index of a product runs slowest
-            return torch.stack([tensors[self._expert(e, which)].t()
+        def stack(which):          # [E, out, in], as stored: the summed index runs fastest
+            return torch.stack([tensors[self._expert(e, which)]
                                 for e in range(self.E)]).contiguous()
         self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
 

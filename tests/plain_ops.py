@@ -226,7 +226,7 @@ class PlainOps:
                 vv[t] = y[2 * HK * D:].to(vv.dtype)
                 row = proj[t].to(self.cd)
                 beta[t] = torch.sigmoid(row[C:C + H]).to(beta.dtype)
-                z = a2.to(self.cd) @ row[C + H:C + H + ra] + dt_bias.to(self.cd)
+                z = row[C + H:C + H + ra] @ a2.to(self.cd) + dt_bias.to(self.cd)     # a2 [ra, H*D]
                 sp = torch.where(z > 30, z, torch.log1p(torch.exp(torch.clamp(z, max=30))))
                 rate = torch.exp(a_log.to(self.cd)).repeat_interleave(D)
                 decay[t] = torch.exp(-rate * sp).to(decay.dtype)
@@ -260,7 +260,7 @@ class PlainOps:
         T = out.shape[0]
         v = o[:T].to(self.cd).view(T, H, V)
         v = v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps) * norm_w.to(self.cd)
-        gate = torch.sigmoid(proj[:T, g_off:g_off + rg].to(self.cd) @ g2.to(self.cd).T)
+        gate = torch.sigmoid(proj[:T, g_off:g_off + rg].to(self.cd) @ g2.to(self.cd))   # [rg, H*V]
         out.copy_((v.view(T, H * V) * gate).to(out.dtype))
 
     def moe_route(self, sel_idx, sel_w, h, w_router, tok_req, *, top, n_groups, keep):
@@ -287,8 +287,8 @@ class PlainOps:
             add = torch.zeros(x.shape[1], dtype=self.cd)
             for k in range(top):
                 e = int(sel_idx[t, k])
-                g = torch.clamp(hv @ w_gate[e].to(self.cd), max=limit)
-                u = torch.clamp(hv @ w_up[e].to(self.cd), min=-limit, max=limit)
+                g = torch.clamp(w_gate[e].to(self.cd) @ hv, max=limit)
+                u = torch.clamp(w_up[e].to(self.cd) @ hv, min=-limit, max=limit)
                 act = g * torch.sigmoid(1.702 * g) * (u + 1.0)
-                add = add + sel_w[t, k].to(self.cd) * (act @ w_down[e].to(self.cd))
+                add = add + sel_w[t, k].to(self.cd) * (w_down[e].to(self.cd) @ act)
             x[t] = (x[t].to(self.cd) + add).to(x.dtype)

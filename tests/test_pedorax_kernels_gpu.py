@@ -160,9 +160,10 @@ def _attend(ops, plain, lat, queries, heads, sink, scale, seed, boost_q=None):
     return got, want
 
 
+@pytest.mark.parametrize("splits", [1, 3, 16])
 @pytest.mark.parametrize("cache_dtype, tol", [(F32, 2e-5), (BF16, 2e-5)])
 @pytest.mark.parametrize("rank, rot, heads", [(24, 8, 3), (72, 4, 11), (130, 16, 1)])
-def test_latent_attention_random(ops, plain, cache_dtype, tol, rank, rot, heads):
+def test_latent_attention_random(ops, plain, cache_dtype, tol, rank, rot, heads, splits):
     """The cache rows are rounded once (by the append, the same in twin and kernel); behind
     that both sides are exact, so the tolerance does not depend on the cache type."""
     lat = _fill(ops, plain, (70, 33), rank, rot, cache_dtype, seed=10)
@@ -170,7 +171,11 @@ def test_latent_attention_random(ops, plain, cache_dtype, tol, rank, rot, heads)
     lat.pool = lat.pool_dev.cpu().clone()          # attend over the very rows the kernel wrote
     queries = [(0, 0), (0, 1), (0, 15), (0, 16), (0, 31), (0, 32), (0, 69), (1, 0), (1, 32),
                (1, 17)]
-    got, want = _attend(ops, plain, lat, queries, heads, rnd(heads, seed=3), 0.2, seed=20)
+    ops.latent_splits = splits          # one block a token, or its keys split over several
+    try:
+        got, want = _attend(ops, plain, lat, queries, heads, rnd(heads, seed=3), 0.2, seed=20)
+    finally:
+        ops.latent_splits = None
     close(got, want, tol)
 
 
@@ -228,9 +233,9 @@ def _delta_weights(shape, seed):
     H, HK, D, V = shape["heads"], shape["kv_heads"], shape["dim"], shape["vdim"]
     C = 2 * HK * D + H * V
     return dict(conv_w=rnd(C, shape["taps"], seed=seed, std=0.6),
-                a2=rnd(H * D, shape["a_rank"], seed=seed + 1, std=0.5),
+                a2=rnd(shape["a_rank"], H * D, seed=seed + 1, std=0.5),
                 dt_bias=rnd(H * D, seed=seed + 2, std=0.5), a_log=rnd(H, seed=seed + 3) - 1.0,
-                g2=rnd(H * V, shape["g_rank"], seed=seed + 4, std=0.5),
+                g2=rnd(shape["g_rank"], H * V, seed=seed + 4, std=0.5),
                 norm_w=rnd(V, seed=seed + 5).abs() + 0.5)
 
 
@@ -378,8 +383,8 @@ def test_experts(ops, plain, dt, tol):
     type before both sides see them, so the tolerance is that of float32 sums."""
     T, width, ff, E, top = 19, 40, 28, 5, 3
     h = rnd(T, width, seed=100).to(dt)
-    wg, wu = rnd(E, width, ff, seed=101, std=0.4).to(dt), rnd(E, width, ff, seed=102, std=0.4).to(dt)
-    wd = rnd(E, ff, width, seed=103, std=0.3).to(dt)
+    wg, wu = rnd(E, ff, width, seed=101, std=0.4).to(dt), rnd(E, ff, width, seed=102, std=0.4).to(dt)
+    wd = rnd(E, width, ff, seed=103, std=0.3).to(dt)
     g = torch.Generator().manual_seed(104)
     idx = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(T)]).to(I32)
     wts = torch.rand(T, top, generator=g)
@@ -394,3 +399,41 @@ def test_experts(ops, plain, dt, tol):
                     limit=0.8)
     close(got, want, tol)
     assert torch.equal(got[3].cpu(), x[3])
+
+
+@pytest.mark.parametrize("T, width, ff, E, top", [(300, 64, 96, 7, 3), (90, 160, 32, 3, 3)])
+def test_experts_sorted_by_expert_on_the_tensor_cores(ops, plain, T, width, ff, E, top):
+    """Enough pairs for the sorted path: segments longer and shorter than a tile, an expert
+    nobody picks, padding tokens.  Both sides see the same bfloat16 inputs; the kernel also
+    rounds the activations to bfloat16, which bounds the agreement."""
+    h = rnd(T, width, seed=110).to(BF16)
+    wg, wu = rnd(E, ff, width, seed=111, std=0.3).to(BF16), rnd(E, ff, width, seed=112, std=0.3).to(BF16)
+    wd = rnd(E, width, ff, seed=113, std=0.3).to(BF16)
+    g = torch.Generator().manual_seed(114)
+    idx = torch.stack([torch.randperm(E - 1, generator=g)[:top] for _ in range(T)]).to(I32)
+    idx[idx == 2] = E - 1                                  # expert 2 stays without tokens
+    idx[:40] = torch.tensor([0, 1, 3][:top], dtype=I32)    # a long segment for expert 0
+    wts = torch.rand(T, top, generator=g)
+    req = torch.zeros(T, dtype=I32)
+    req[[3, 77]] = -1
+    x = rnd(T, width, seed=115)
+    want = x.double().clone()
+    plain.moe_experts(want, None, h, wg, wu, wd, idx, wts, req, limit=1.5)
+    got = dev(x.clone())
+    y = torch.zeros(T * top, ff, dtype=F32, device=DEV)
+    assert ops.sorted_experts
+    before = ops.launches
+    ops.moe_experts(got, y, dev(h), dev(wg), dev(wu), dev(wd), dev(idx), dev(wts), dev(req),
+                    limit=1.5)
+    assert ops.launches - before == 4                      # sort, two tile kernels, combine
+    scale = (want - x.double()).abs().max().item()
+    close(got, want, 1e-2 * scale)
+    assert torch.equal(got[3].cpu(), x[3]) and torch.equal(got[77].cpu(), x[77])
+    ops.sorted_experts, ops._moe_need = False, {}
+    try:
+        rows = dev(x.clone())
+        ops.moe_experts(rows, y, dev(h), dev(wg), dev(wu), dev(wd), dev(idx), dev(wts), dev(req),
+                        limit=1.5)
+    finally:
+        ops.sorted_experts, ops._moe_need = True, {}
+    close(rows, want, 1e-4 * scale)
