@@ -35,7 +35,7 @@ __device__ __forceinline__ int channels(const DeltaShape& s) {
   return 2 * s.kv_heads * s.D + s.heads * s.V;
 }
 
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(512)
 delta_prepare_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __restrict__ vv,
                      float* __restrict__ beta, float* __restrict__ decay,
                      const float* __restrict__ proj, const float* __restrict__ conv_w,
@@ -54,6 +54,7 @@ delta_prepare_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __re
   const int hist = s.taps - 1;
   for (int c = threadIdx.x; c < C; c += blockDim.x) {
     float acc = 0.f;
+#pragma unroll 4
     for (int j = 0; j < s.taps; ++j) {
       const int local = l - (hist - j);
       const float in = local >= 0 ? proj[(size_t)(first + local) * s.stride + c]
@@ -85,6 +86,7 @@ delta_prepare_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __re
   const int HD = s.heads * s.D;
   for (int i = threadIdx.x; i < HD; i += blockDim.x) {
     float z = 0.f;
+#pragma unroll 8
     for (int k = 0; k < s.ra; ++k) z = fmaf(a2[(size_t)k * HD + i], row[s.a_off + k], z);
     z += dt_bias[i];
     decay[(size_t)t * HD + i] = expf(-expf(A_log[i / s.D]) * softplusf_(z));
@@ -113,35 +115,41 @@ __global__ void delta_conv_state_kernel(float* __restrict__ state, const float* 
   }
 }
 
-constexpr int DR_DP = 8;          // state rows a thread keeps
-constexpr int DR_THREADS = 128;
+constexpr int DR_DP = 16;         // state rows a thread keeps
+constexpr int DR_THREADS = 256;
+
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+  const unsigned sa = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(sa), "l"(src));
+}
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+  const unsigned sa = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(src));
+}
 
 // Thread (col, part) keeps rows part*DP .. part*DP+DP-1 of column col of S; the KS parts of a
 // column are neighbouring lanes and sum their shares with a butterfly.  The tokens' q, k, decay
 // rows (padded with zeros to KS*DP), v columns and betas come through shared memory a chunk of
-// CH tokens at a time, so that the latency of fetching them is paid once a chunk, not once a
-// token.
+// CH tokens at a time, fetched asynchronously while the chunk before is worked on: the latency
+// of fetching them is off the token-to-token chain.
 __global__ void __launch_bounds__(DR_THREADS)
 delta_recurrence_kernel(float* __restrict__ o, float* __restrict__ state,
                         const float* __restrict__ qn, const float* __restrict__ kn,
                         const float* __restrict__ vv, const float* __restrict__ beta,
                         const float* __restrict__ decay, const int* __restrict__ req_start,
                         const int* __restrict__ req_len, const int* __restrict__ req_slot,
-                        DeltaShape s, int KS, int CH) {
+                        DeltaShape s, int KS, int CH, int vec) {
   extern __shared__ __align__(16) float sm[];
   const int r = blockIdx.x, h = blockIdx.y;
   const int n = req_len[r];
   if (n <= 0) return;
   const int Dp = KS * DR_DP;
   const int cols = DR_THREADS / KS;
-  float* s_k = sm;
-  float* s_q = s_k + CH * Dp;
-  float* s_g = s_q + CH * Dp;
-  float* s_v = s_g + CH * Dp;
-  float* s_b = s_v + CH * cols;
+  const int per_buf = (3 * CH * Dp + CH * cols + CH + 3) & ~3;      // buffers 16-byte aligned
   const int part = threadIdx.x % KS;
   const int lc = threadIdx.x / KS;
-  const int col = blockIdx.z * cols + lc;
+  const int col0 = blockIdx.z * cols;
+  const int col = col0 + lc;
   const bool col_ok = col < s.V;
   const int kh = h / (s.heads / s.kv_heads);
   const int d0 = part * DR_DP;
@@ -152,82 +160,125 @@ delta_recurrence_kernel(float* __restrict__ o, float* __restrict__ state,
     st[i] = (col_ok && d0 + i < s.D) ? S[(size_t)(d0 + i) * s.V + col] : 0.f;
   const int QK = s.kv_heads * s.D, HV = s.heads * s.V, HD = s.heads * s.D;
   const int first = req_start[r];
-  for (int c0 = 0; c0 < n; c0 += CH) {
+  for (int i = threadIdx.x; i < 2 * per_buf; i += DR_THREADS) sm[i] = 0.f;   // the padding stays 0
+  __syncthreads();
+  auto fetch = [&](int buf, int c0) {
+    float* b_k = sm + buf * per_buf;
+    float* b_q = b_k + CH * Dp;
+    float* b_g = b_q + CH * Dp;
+    float* b_v = b_g + CH * Dp;
+    float* b_b = b_v + CH * cols;
     const int nc = min(CH, n - c0);
-    __syncthreads();                               // the chunk before has been used
-    for (int i = threadIdx.x; i < nc * Dp; i += DR_THREADS) {
-      const int tt = i / Dp, d = i - tt * Dp;
-      const size_t row = first + c0 + tt;
-      const bool ok = d < s.D;
-      s_k[i] = ok ? kn[row * QK + kh * s.D + d] : 0.f;
-      s_q[i] = ok ? qn[row * QK + kh * s.D + d] : 0.f;
-      s_g[i] = ok ? decay[row * HD + h * s.D + d] : 0.f;
+    if (vec) {
+      const int D4 = s.D >> 2;
+      for (int i = threadIdx.x; i < nc * D4; i += DR_THREADS) {
+        const int tt = i / D4, d = (i - tt * D4) * 4;
+        const size_t row = first + c0 + tt;
+        cp_async16(b_k + tt * Dp + d, kn + row * QK + kh * s.D + d);
+        cp_async16(b_q + tt * Dp + d, qn + row * QK + kh * s.D + d);
+        cp_async16(b_g + tt * Dp + d, decay + row * HD + h * s.D + d);
+      }
+    } else {
+      for (int i = threadIdx.x; i < nc * s.D; i += DR_THREADS) {
+        const int tt = i / s.D, d = i - tt * s.D;
+        const size_t row = first + c0 + tt;
+        cp_async4(b_k + tt * Dp + d, kn + row * QK + kh * s.D + d);
+        cp_async4(b_q + tt * Dp + d, qn + row * QK + kh * s.D + d);
+        cp_async4(b_g + tt * Dp + d, decay + row * HD + h * s.D + d);
+      }
     }
     for (int i = threadIdx.x; i < nc * cols; i += DR_THREADS) {
       const int tt = i / cols, cc = i - tt * cols;
-      const int cg = blockIdx.z * cols + cc;
-      s_v[i] = cg < s.V ? vv[(size_t)(first + c0 + tt) * HV + h * s.V + cg] : 0.f;
+      if (col0 + cc < s.V)
+        cp_async4(b_v + i, vv + (size_t)(first + c0 + tt) * HV + h * s.V + col0 + cc);
     }
-    if (threadIdx.x < nc) s_b[threadIdx.x] = beta[(size_t)(first + c0 + threadIdx.x) * s.heads + h];
+    if (threadIdx.x < nc)
+      cp_async4(b_b + threadIdx.x, beta + (size_t)(first + c0 + threadIdx.x) * s.heads + h);
+    asm volatile("cp.async.commit_group;");
+  };
+  fetch(0, 0);
+  int buf = 0;
+  for (int c0 = 0; c0 < n; c0 += CH, buf ^= 1) {
+    const int nc = min(CH, n - c0);
+    if (c0 + CH < n) {
+      fetch(buf ^ 1, c0 + CH);
+      asm volatile("cp.async.wait_group 1;");
+    } else {
+      asm volatile("cp.async.wait_group 0;");
+    }
     __syncthreads();
+    const float* b_k = sm + buf * per_buf;
+    const float* b_q = b_k + CH * Dp;
+    const float* b_g = b_q + CH * Dp;
+    const float* b_v = b_g + CH * Dp;
+    const float* b_b = b_v + CH * cols;
     for (int tt = 0; tt < nc; ++tt) {
-      const float4* k4 = (const float4*)(s_k + tt * Dp + d0);
-      const float4* q4 = (const float4*)(s_q + tt * Dp + d0);
-      const float4* g4 = (const float4*)(s_g + tt * Dp + d0);
-      float kk[DR_DP], qq[DR_DP], gg[DR_DP];
+      const float4* k4 = (const float4*)(b_k + tt * Dp + d0);
+      const float4* q4 = (const float4*)(b_q + tt * Dp + d0);
+      const float4* g4 = (const float4*)(b_g + tt * Dp + d0);
+      float kk[DR_DP], qq[DR_DP];
+      float dot0 = 0.f, dot1 = 0.f;
 #pragma unroll
       for (int j = 0; j < DR_DP / 4; ++j) {
         const float4 a = k4[j], b = q4[j], c = g4[j];
         kk[4 * j] = a.x; kk[4 * j + 1] = a.y; kk[4 * j + 2] = a.z; kk[4 * j + 3] = a.w;
         qq[4 * j] = b.x; qq[4 * j + 1] = b.y; qq[4 * j + 2] = b.z; qq[4 * j + 3] = b.w;
-        gg[4 * j] = c.x; gg[4 * j + 1] = c.y; gg[4 * j + 2] = c.z; gg[4 * j + 3] = c.w;
+        st[4 * j] *= c.x; st[4 * j + 1] *= c.y; st[4 * j + 2] *= c.z; st[4 * j + 3] *= c.w;
+        dot0 = fmaf(st[4 * j], a.x, dot0); dot1 = fmaf(st[4 * j + 1], a.y, dot1);
+        dot0 = fmaf(st[4 * j + 2], a.z, dot0); dot1 = fmaf(st[4 * j + 3], a.w, dot1);
       }
-      float dot = 0.f;
-#pragma unroll
-      for (int j = 0; j < DR_DP; ++j) {
-        st[j] *= gg[j];
-        dot = fmaf(st[j], kk[j], dot);
-      }
+      float dot = dot0 + dot1;
       for (int off = 1; off < KS; off <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
-      const float u = s_b[tt] * (s_v[tt * cols + lc] - dot);
-      float out = 0.f;
+      const float u = b_b[tt] * (b_v[tt * cols + lc] - dot);
+      float out0 = 0.f, out1 = 0.f;
 #pragma unroll
-      for (int j = 0; j < DR_DP; ++j) {
+      for (int j = 0; j < DR_DP; j += 2) {
         st[j] = fmaf(kk[j], u, st[j]);
-        out = fmaf(st[j], qq[j], out);
+        st[j + 1] = fmaf(kk[j + 1], u, st[j + 1]);
+        out0 = fmaf(st[j], qq[j], out0);
+        out1 = fmaf(st[j + 1], qq[j + 1], out1);
       }
+      float out = out0 + out1;
       for (int off = 1; off < KS; off <<= 1) out += __shfl_xor_sync(0xffffffffu, out, off);
       if (part == 0 && col_ok) o[(size_t)(first + c0 + tt) * HV + h * s.V + col] = out;
     }
+    __syncthreads();                              // this buffer is fetched into again next turn
   }
 #pragma unroll
   for (int i = 0; i < DR_DP; ++i)
     if (col_ok && d0 + i < s.D) S[(size_t)(d0 + i) * s.V + col] = st[i];
 }
 
+// One block per token and head: the head's root mean square by a block reduction, then one
+// thread per output forms its gate (a sum over the rg inputs, several loads in flight).
 template <typename TO>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 delta_finish_kernel(TO* __restrict__ out, const float* __restrict__ o,
                     const float* __restrict__ proj, const float* __restrict__ g2,
                     const float* __restrict__ norm_w, const int* __restrict__ tok_req,
                     float eps, DeltaShape s) {
-  const int t = blockIdx.x;
+  __shared__ float red[4];
+  extern __shared__ float s_gin[];                  // [rg]
+  const int t = blockIdx.x, h = blockIdx.y;
   if (tok_req[t] < 0) return;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const int HV = s.heads * s.V;
   const float* gin = proj + (size_t)t * s.stride + s.g_off;
-  for (int h = warp; h < s.heads; h += nw) {
-    const float* src = o + (size_t)t * HV + (size_t)h * s.V;
-    float ss = 0.f;
-    for (int e = lane; e < s.V; e += 32) ss = fmaf(src[e], src[e], ss);
-    ss = warp_sum(ss);
-    const float inv = 1.0f / sqrtf(ss / (float)s.V + eps);
-    for (int e = lane; e < s.V; e += 32) {
-      const float* gcol = g2 + (size_t)h * s.V + e;
-      float z = 0.f;
-      for (int k = 0; k < s.rg; ++k) z = fmaf(gcol[(size_t)k * HV], gin[k], z);
-      out[(size_t)t * HV + h * s.V + e] = from_f<TO>(src[e] * inv * norm_w[e] * sigmoidf_(z));
-    }
+  for (int k = threadIdx.x; k < s.rg; k += blockDim.x) s_gin[k] = gin[k];
+  const float* src = o + (size_t)t * HV + (size_t)h * s.V;
+  float ss = 0.f;
+  for (int e = threadIdx.x; e < s.V; e += blockDim.x) ss = fmaf(src[e], src[e], ss);
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += red[i];
+  const float inv = 1.0f / sqrtf(tot / (float)s.V + eps);
+  for (int e = threadIdx.x; e < s.V; e += blockDim.x) {
+    const float* gcol = g2 + (size_t)h * s.V + e;
+    float z = 0.f;
+#pragma unroll 8
+    for (int k = 0; k < s.rg; ++k) z = fmaf(gcol[(size_t)k * HV], s_gin[k], z);
+    out[(size_t)t * HV + h * s.V + e] = from_f<TO>(src[e] * inv * norm_w[e] * sigmoidf_(z));
   }
 }
 
@@ -270,7 +321,7 @@ HS_EXPORT int hs_delta_prepare(float* qn, float* kn, float* vv, float* beta, flo
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(hs::delta_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          (int)smem);
-  hs::delta_prepare_kernel<<<n_tokens, 256, smem, st>>>(qn, kn, vv, beta, decay, proj, conv_w, a2,
+  hs::delta_prepare_kernel<<<n_tokens, 512, smem, st>>>(qn, kn, vv, beta, decay, proj, conv_w, a2,
                                                         dt_bias, A_log, state, tok_req, req_start,
                                                         req_slot, s);
   HS_LAUNCH_CHECK();
@@ -292,16 +343,21 @@ HS_EXPORT int hs_delta_recurrence(float* o, float* state, const float* qn, const
   hs::DeltaShape s;
   int rc = delta_shape(&s, heads, kv_heads, D, V, taps, ra, rg);
   if (rc) return rc;
-  if (D > hs::DR_DP * 32) return HS_ERR_UNSUPPORTED;
+  if (D > hs::DR_DP * 32) return HS_ERR_UNSUPPORTED;   // a column's parts are lanes of one warp
   if (n_requests <= 0) return HS_OK;
   int KS = 1;
   while (KS * hs::DR_DP < D) KS <<= 1;
   const int cols = hs::DR_THREADS / KS;
-  const int CH = KS * hs::DR_DP <= 128 ? 16 : 8;
-  const size_t smem = (size_t)(3 * CH * KS * hs::DR_DP + CH * cols + CH) * sizeof(float);
+  const int Dp = KS * hs::DR_DP;
+  int CH = 1024 / Dp;                               // tokens a chunk: 3 * CH * Dp <= 3072 floats
+  CH = CH < 2 ? 2 : (CH > 16 ? 16 : CH);
+  const size_t smem = 2 * (size_t)((3 * CH * Dp + CH * cols + CH + 3) & ~3) * sizeof(float);
+  // 16-byte copies need rows of q, k and the decay that start on 16-byte boundaries
+  const int vec = D % 4 == 0 && !((uintptr_t)qn & 15) && !((uintptr_t)kn & 15) &&
+                  !((uintptr_t)decay & 15);
   dim3 grid(n_requests, heads, (V + cols - 1) / cols);
   hs::delta_recurrence_kernel<<<grid, hs::DR_THREADS, smem, (cudaStream_t)stream>>>(
-      o, state, qn, kn, vv, beta, decay, req_start, req_len, req_slot, s, KS, CH);
+      o, state, qn, kn, vv, beta, decay, req_start, req_len, req_slot, s, KS, CH, vec);
   HS_LAUNCH_CHECK();
   return HS_OK;
 }
@@ -317,10 +373,10 @@ HS_EXPORT int hs_delta_finish(void* out, const float* o, const float* proj, cons
   if (n_tokens <= 0) return HS_OK;
   cudaStream_t st = (cudaStream_t)stream;
   if (out_dtype == HS_DT_F32)
-    hs::delta_finish_kernel<float><<<n_tokens, 256, 0, st>>>((float*)out, o, proj, g2, norm_w,
-                                                             tok_req, eps, s);
+    hs::delta_finish_kernel<float><<<dim3(n_tokens, heads), 128, rg * sizeof(float), st>>>(
+        (float*)out, o, proj, g2, norm_w, tok_req, eps, s);
   else if (out_dtype == HS_DT_BF16)
-    hs::delta_finish_kernel<__nv_bfloat16><<<n_tokens, 256, 0, st>>>(
+    hs::delta_finish_kernel<__nv_bfloat16><<<dim3(n_tokens, heads), 128, rg * sizeof(float), st>>>(
         (__nv_bfloat16*)out, o, proj, g2, norm_w, tok_req, eps, s);
   else
     return HS_ERR_UNSUPPORTED;

@@ -34,6 +34,7 @@ grouped_linear_kernel(TO* __restrict__ out, const float* __restrict__ a,
 #pragma unroll
   for (int tt = 0; tt < GL_TT; ++tt) acc[tt] = 0.f;
   const TW* wg = w + (size_t)g * k * n + j;
+#pragma unroll 8
   for (int kk = 0; kk < k; ++kk) {
     const float wv = to_f(wg[(size_t)kk * n]);
 #pragma unroll

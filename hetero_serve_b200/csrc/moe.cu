@@ -29,7 +29,43 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
   }
 }
 
-constexpr int ROUTE_THREADS = 128;
+// -- path 1: a matrix-vector product per pair ---------------------------------------------------
+// dot of a weight row (n contiguous values) with a float32 vector in shared memory, over a warp
+__device__ __forceinline__ float row_dot(const float* __restrict__ w, const float* v, int n,
+                                         int lane) {
+  float acc = 0.f;
+  if ((n & 3) == 0 && (((uintptr_t)w) & 15) == 0) {
+    for (int k = lane * 4; k < n; k += 128) {
+      const float4 a = *(const float4*)(w + k);
+      acc = fmaf(a.x, v[k], acc); acc = fmaf(a.y, v[k + 1], acc);
+      acc = fmaf(a.z, v[k + 2], acc); acc = fmaf(a.w, v[k + 3], acc);
+    }
+  } else {
+    for (int k = lane; k < n; k += 32) acc = fmaf(w[k], v[k], acc);
+  }
+  return warp_sum(acc);
+}
+__device__ __forceinline__ float row_dot(const __nv_bfloat16* __restrict__ w, const float* v,
+                                         int n, int lane) {
+  float acc = 0.f;
+  if ((n & 7) == 0 && (((uintptr_t)w) & 15) == 0) {
+    for (int k = lane * 8; k < n; k += 256) {
+      const uint4 raw = *(const uint4*)(w + k);
+      const __nv_bfloat162* p = (const __nv_bfloat162*)&raw;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(p[i]);
+        acc = fmaf(f.x, v[k + 2 * i], acc);
+        acc = fmaf(f.y, v[k + 2 * i + 1], acc);
+      }
+    }
+  } else {
+    for (int k = lane; k < n; k += 32) acc = fmaf(__bfloat162float(w[k]), v[k], acc);
+  }
+  return warp_sum(acc);
+}
+
+constexpr int ROUTE_THREADS = 256;
 
 // One block per token: the warps share the experts' dot products, warp 0 then chooses.
 template <typename TH>
@@ -48,9 +84,7 @@ moe_route_kernel(int* __restrict__ sel_idx, float* __restrict__ sel_w, const TH*
   __syncthreads();
   for (int e = warp; e < E; e += ROUTE_THREADS / 32) {
     const float* wr = w_router + (size_t)e * width;
-    float z = 0.f;
-    for (int k = lane; k < width; k += 32) z = fmaf(wr[k], s_h[k], z);
-    z = warp_sum(z);
+    const float z = row_dot(wr, s_h, width, lane);
     if (lane == 0) s_s[e] = 1.0f / (1.0f + expf(-z));
   }
   __syncthreads();
@@ -102,42 +136,7 @@ __device__ __forceinline__ float expert_act(float g, float u, float limit) {
   return g * (1.0f / (1.0f + expf(-1.702f * g))) * (u + 1.0f);
 }
 
-// -- path 1: a matrix-vector product per pair ---------------------------------------------------
-// dot of a weight row (n contiguous values) with a float32 vector in shared memory, over a warp
-__device__ __forceinline__ float row_dot(const float* __restrict__ w, const float* v, int n,
-                                         int lane) {
-  float acc = 0.f;
-  if ((n & 3) == 0 && (((uintptr_t)w) & 15) == 0) {
-    for (int k = lane * 4; k < n; k += 128) {
-      const float4 a = *(const float4*)(w + k);
-      acc = fmaf(a.x, v[k], acc); acc = fmaf(a.y, v[k + 1], acc);
-      acc = fmaf(a.z, v[k + 2], acc); acc = fmaf(a.w, v[k + 3], acc);
-    }
-  } else {
-    for (int k = lane; k < n; k += 32) acc = fmaf(w[k], v[k], acc);
-  }
-  return warp_sum(acc);
-}
-__device__ __forceinline__ float row_dot(const __nv_bfloat16* __restrict__ w, const float* v,
-                                         int n, int lane) {
-  float acc = 0.f;
-  if ((n & 7) == 0 && (((uintptr_t)w) & 15) == 0) {
-    for (int k = lane * 8; k < n; k += 256) {
-      const uint4 raw = *(const uint4*)(w + k);
-      const __nv_bfloat162* p = (const __nv_bfloat162*)&raw;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float2 f = __bfloat1622float2(p[i]);
-        acc = fmaf(f.x, v[k + 2 * i], acc);
-        acc = fmaf(f.y, v[k + 2 * i + 1], acc);
-      }
-    }
-  } else {
-    for (int k = lane; k < n; k += 32) acc = fmaf(__bfloat162float(w[k]), v[k], acc);
-  }
-  return warp_sum(acc);
-}
-
+// a matrix-vector product per pair: rows of the expert, one warp each
 constexpr int GEMV_THREADS = 256;
 constexpr int GEMV_ROWS = 32;       // output rows a block covers
 

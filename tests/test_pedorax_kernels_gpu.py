@@ -283,6 +283,8 @@ def _delta_run(o_ops, shape, w, proj, state, portions, slots, device):
     dict(heads=2, kv_heads=1, dim=72, vdim=40, taps=3, a_rank=2, g_rank=9),     # 16 lanes a column
     dict(heads=3, kv_heads=3, dim=8, vdim=8, taps=1, a_rank=4, g_rank=4),       # no history
     dict(heads=1, kv_heads=1, dim=200, vdim=5, taps=2, a_rank=3, g_rank=3),
+    dict(heads=2, kv_heads=2, dim=10, vdim=6, taps=2, a_rank=3, g_rank=2),      # rows not 16-byte
+    dict(heads=1, kv_heads=1, dim=300, vdim=40, taps=2, a_rank=3, g_rank=2),    # two tokens a chunk
 ])
 def test_delta_rule_in_portions_equals_the_whole(ops, plain, shape):
     """Two requests in slots 2 and 0 of three, cut into portions shorter than the convolution's
@@ -401,7 +403,7 @@ def test_experts(ops, plain, dt, tol):
     assert torch.equal(got[3].cpu(), x[3])
 
 
-@pytest.mark.parametrize("T, width, ff, E, top", [(300, 64, 96, 7, 3), (90, 160, 32, 3, 3)])
+@pytest.mark.parametrize("T, width, ff, E, top", [(300, 64, 96, 7, 3), (90, 160, 32, 4, 3)])
 def test_experts_sorted_by_expert_on_the_tensor_cores(ops, plain, T, width, ff, E, top):
     """Enough pairs for the sorted path: segments longer and shorter than a tile, an expert
     nobody picks, padding tokens.  Both sides see the same bfloat16 inputs; the kernel also
