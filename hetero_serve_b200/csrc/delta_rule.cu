@@ -127,8 +127,10 @@ __device__ __forceinline__ void cp_async16(float* dst, const float* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(src));
 }
 
-// Thread (col, part) keeps rows part*DP .. part*DP+DP-1 of column col of S; the KS parts of a
-// column are neighbouring lanes and sum their shares with a butterfly.  The tokens' q, k, decay
+// Thread (col, part) keeps DP rows of column col of S: the four rows 4*part + 4*KS*j .. + 3 for
+// j = 0 .. DP/4 - 1, so that the KS neighbouring lanes of a column read neighbouring 16-byte
+// pieces of a row in shared memory (no bank conflict); they sum their shares with a butterfly.
+// The tokens' q, k, decay
 // rows (padded with zeros to KS*DP), v columns and betas come through shared memory a chunk of
 // CH tokens at a time, fetched asynchronously while the chunk before is worked on: the latency
 // of fetching them is off the token-to-token chain.
@@ -152,12 +154,15 @@ delta_recurrence_kernel(float* __restrict__ o, float* __restrict__ state,
   const int col = col0 + lc;
   const bool col_ok = col < s.V;
   const int kh = h / (s.heads / s.kv_heads);
-  const int d0 = part * DR_DP;
+  const int d0 = part * 4;                       // row of st[i]: d0 + 4*KS*(i/4) + i%4
+  const int dj = 4 * KS;
   float* S = state + (size_t)req_slot[r] * s.state_stride + (size_t)h * s.D * s.V;
   float st[DR_DP];
 #pragma unroll
-  for (int i = 0; i < DR_DP; ++i)
-    st[i] = (col_ok && d0 + i < s.D) ? S[(size_t)(d0 + i) * s.V + col] : 0.f;
+  for (int i = 0; i < DR_DP; ++i) {
+    const int d = d0 + dj * (i >> 2) + (i & 3);
+    st[i] = (col_ok && d < s.D) ? S[(size_t)d * s.V + col] : 0.f;
+  }
   const int QK = s.kv_heads * s.D, HV = s.heads * s.V, HD = s.heads * s.D;
   const int first = req_start[r];
   for (int i = threadIdx.x; i < 2 * per_buf; i += DR_THREADS) sm[i] = 0.f;   // the padding stays 0
@@ -220,7 +225,7 @@ delta_recurrence_kernel(float* __restrict__ o, float* __restrict__ state,
       float dot0 = 0.f, dot1 = 0.f;
 #pragma unroll
       for (int j = 0; j < DR_DP / 4; ++j) {
-        const float4 a = k4[j], b = q4[j], c = g4[j];
+        const float4 a = k4[j * KS], b = q4[j * KS], c = g4[j * KS];
         kk[4 * j] = a.x; kk[4 * j + 1] = a.y; kk[4 * j + 2] = a.z; kk[4 * j + 3] = a.w;
         qq[4 * j] = b.x; qq[4 * j + 1] = b.y; qq[4 * j + 2] = b.z; qq[4 * j + 3] = b.w;
         st[4 * j] *= c.x; st[4 * j + 1] *= c.y; st[4 * j + 2] *= c.z; st[4 * j + 3] *= c.w;
@@ -245,8 +250,10 @@ delta_recurrence_kernel(float* __restrict__ o, float* __restrict__ state,
     __syncthreads();                              // this buffer is fetched into again next turn
   }
 #pragma unroll
-  for (int i = 0; i < DR_DP; ++i)
-    if (col_ok && d0 + i < s.D) S[(size_t)(d0 + i) * s.V + col] = st[i];
+  for (int i = 0; i < DR_DP; ++i) {
+    const int d = d0 + dj * (i >> 2) + (i & 3);
+    if (col_ok && d < s.D) S[(size_t)d * s.V + col] = st[i];
+  }
 }
 
 // One block per token and head: the head's root mean square by a block reduction, then one

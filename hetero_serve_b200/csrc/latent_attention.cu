@@ -60,7 +60,14 @@ __global__ void latent_append_kernel(TC* __restrict__ pool, const float* __restr
 constexpr int LA_TILE = 32;     // keys per tile: one per lane when scores are formed
 constexpr int LA_HB = 8;        // heads (warps) per block
 
-template <typename TC, int RC>
+// Shared rows are padded to a multiple of 4 floats (zeros), read 16 bytes at a time.  Key rows
+// have a stride of 4 (mod 32) floats, so that the lanes of a quarter warp, each on a row of its
+// own while scores are formed, hit distinct banks; while the weighted rows are summed, lane l
+// owns the dims 4 l + 128 i .. + 3 and the lanes read neighbouring pieces of one row.
+__host__ __device__ inline int la_w4(int W) { return (W + 3) & ~3; }
+__host__ __device__ inline int la_stride(int W) { return ((la_w4(W) + 27) / 32) * 32 + 4; }
+
+template <typename TC, int RC>      // RC: accumulator floats a lane keeps, a multiple of 4
 __global__ void __launch_bounds__(LA_HB * 32)
 latent_attention_kernel(float* __restrict__ out, const float* __restrict__ qa,
                         const float* __restrict__ qr, const TC* __restrict__ pool,
@@ -69,11 +76,11 @@ latent_attention_kernel(float* __restrict__ out, const float* __restrict__ qa,
                         int n_heads, int R, int P, int qr_stride, int qr_hstride, int qr_off,
                         float scale, int page_size, int num_pages, int max_pages, int* status,
                         int nsplit, float* __restrict__ partial) {
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   const int W = R + P;
-  const int ks = W | 1;                         // odd row stride: lanes on rows hit distinct banks
-  float* s_q = smem;                            // [LA_HB][W]
-  float* s_k = smem + LA_HB * W;                // [LA_TILE][ks]
+  const int W4 = la_w4(W), ks = la_stride(W);
+  float* s_q = smem;                            // [LA_HB][W4]
+  float* s_k = smem + LA_HB * W4;               // [LA_TILE][ks]
   const int t = blockIdx.x;
   const int r = tok_req[t];
   if (r < 0) return;
@@ -82,11 +89,11 @@ latent_attention_kernel(float* __restrict__ out, const float* __restrict__ qa,
   const int h = blockIdx.y * LA_HB + warp;
   const bool live = h < n_heads;
   // queries of this block's heads
-  for (int i = threadIdx.x; i < LA_HB * W; i += blockDim.x) {
-    const int hh = i / W, d = i - hh * W;
+  for (int i = threadIdx.x; i < LA_HB * W4; i += blockDim.x) {
+    const int hh = i / W4, d = i - hh * W4;
     const int head = blockIdx.y * LA_HB + hh;
     float v = 0.f;
-    if (head < n_heads)
+    if (head < n_heads && d < W)
       v = d < R ? qa[((size_t)t * n_heads + head) * R + d]
                 : qr[(size_t)t * qr_stride + (size_t)head * qr_hstride + qr_off + (d - R)];
     s_q[i] = v;
@@ -98,7 +105,7 @@ latent_attention_kernel(float* __restrict__ out, const float* __restrict__ qa,
   float acc[RC];
 #pragma unroll
   for (int i = 0; i < RC; ++i) acc[i] = 0.f;
-  const float* q = s_q + warp * W;
+  const float4* q4 = (const float4*)(s_q + warp * W4);
   const int n_tiles = pos / LA_TILE + 1;
   const int per = (n_tiles + nsplit - 1) / nsplit;
   const int tile_lo = blockIdx.z * per, tile_hi = min(n_tiles, tile_lo + per);
@@ -112,20 +119,24 @@ latent_attention_kernel(float* __restrict__ out, const float* __restrict__ qa,
       float* dst = s_k + j * ks;
       if (page < 0 || page >= num_pages) {
         if (lane == 0) atomicOr(status, HS_STATUS_BAD_PAGE);
-        for (int d = lane; d < W; d += 32) dst[d] = 0.f;
+        for (int d = lane; d < W4; d += 32) dst[d] = 0.f;
       } else {
         const TC* src = pool + ((size_t)page * page_size + (kp % page_size)) * W;
-        for (int d = lane; d < W; d += 32) dst[d] = to_f(src[d]);
+        for (int d = lane; d < W4; d += 32) dst[d] = d < W ? to_f(src[d]) : 0.f;
       }
     }
     __syncthreads();
     if (!live) continue;
     float s = -INFINITY;
     if (lane < nk) {
-      const float* kr = s_k + lane * ks;
-      float dot = 0.f;
-      for (int d = 0; d < W; ++d) dot = fmaf(q[d], kr[d], dot);
-      s = dot * scale;
+      const float4* k4 = (const float4*)(s_k + lane * ks);
+      float d0 = 0.f, d1 = 0.f;
+      for (int d = 0; d < W4 / 4; ++d) {
+        const float4 a = q4[d], b = k4[d];
+        d0 = fmaf(a.x, b.x, d0); d1 = fmaf(a.y, b.y, d1);
+        d0 = fmaf(a.z, b.z, d0); d1 = fmaf(a.w, b.w, d1);
+      }
+      s = (d0 + d1) * scale;
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float corr = expf(m - m_new);
@@ -136,31 +147,34 @@ latent_attention_kernel(float* __restrict__ out, const float* __restrict__ qa,
     for (int i = 0; i < RC; ++i) acc[i] *= corr;
     for (int j = 0; j < nk; ++j) {
       const float w = __shfl_sync(0xffffffffu, pj, j);
-      const float* kr = s_k + j * ks;
+      const float* kr = s_k + j * ks + 4 * lane;
 #pragma unroll
-      for (int i = 0; i < RC; ++i) {
-        const int d = lane + 32 * i;
-        if (d < R) acc[i] = fmaf(w, kr[d], acc[i]);
+      for (int i = 0; i < RC / 4; ++i) {
+        if (4 * lane + 128 * i < R) {           // the piece lies within the padded row
+          const float4 c = *(const float4*)(kr + 128 * i);
+          acc[4 * i] = fmaf(w, c.x, acc[4 * i]);
+          acc[4 * i + 1] = fmaf(w, c.y, acc[4 * i + 1]);
+          acc[4 * i + 2] = fmaf(w, c.z, acc[4 * i + 2]);
+          acc[4 * i + 3] = fmaf(w, c.w, acc[4 * i + 3]);
+        }
       }
     }
   }
   if (!live) return;
+  float* dst;
+  float inv = 1.f;
   if (nsplit > 1) {                             // this block's share: maximum, sum, weighted rows
     float* ps = partial + (((size_t)t * n_heads + h) * nsplit + blockIdx.z) * (R + 2);
     if (lane == 0) { ps[0] = m; ps[1] = l; }
-#pragma unroll
-    for (int i = 0; i < RC; ++i) {
-      const int d = lane + 32 * i;
-      if (d < R) ps[2 + d] = acc[i];
-    }
-    return;
+    dst = ps + 2;
+  } else {
+    inv = 1.0f / l;
+    dst = out + ((size_t)t * n_heads + h) * R;
   }
-  const float inv = 1.0f / l;
-  float* o = out + ((size_t)t * n_heads + h) * R;
 #pragma unroll
   for (int i = 0; i < RC; ++i) {
-    const int d = lane + 32 * i;
-    if (d < R) o[d] = acc[i] * inv;
+    const int d = 4 * lane + 128 * (i >> 2) + (i & 3);
+    if (d < R) dst[d] = acc[i] * inv;
   }
 }
 
@@ -224,7 +238,8 @@ static int launch_latent_attention(float* out, const float* qa, const float* qr,
                                    int page_size, int num_pages, int max_pages, int* status,
                                    int nsplit, float* partial, cudaStream_t st) {
   const int W = R + P;
-  const size_t smem = ((size_t)hs::LA_HB * W + (size_t)hs::LA_TILE * (W | 1)) * sizeof(float);
+  const size_t smem = ((size_t)hs::LA_HB * hs::la_w4(W) + (size_t)hs::LA_TILE * hs::la_stride(W)) *
+                      sizeof(float);
   if (smem > 200 * 1024) return HS_ERR_UNSUPPORTED;
   auto kern = hs::latent_attention_kernel<TC, RC>;
   if (smem > 48 * 1024)
@@ -263,7 +278,6 @@ HS_EXPORT int hs_latent_attention(float* out, const float* qa, const float* qr, 
                                          status, nsplit, partial, st)
 #define HS_LA_RC(TC)                   \
   do {                                 \
-    if (rc <= 2) HS_LA(TC, 2);         \
     if (rc <= 4) HS_LA(TC, 4);         \
     if (rc <= 8) HS_LA(TC, 8);         \
     HS_LA(TC, 16);                     \
