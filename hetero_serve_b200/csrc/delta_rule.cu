@@ -35,7 +35,9 @@ __device__ __forceinline__ int channels(const DeltaShape& s) {
   return 2 * s.kv_heads * s.D + s.heads * s.V;
 }
 
-__global__ void __launch_bounds__(512)
+// Three blocks a token (blockIdx.y): 0 convolves q and k and makes them unit vectors, 1 convolves
+// v and forms beta, 2 forms the decay.  They share nothing.
+__global__ void __launch_bounds__(256)
 delta_prepare_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __restrict__ vv,
                      float* __restrict__ beta, float* __restrict__ decay,
                      const float* __restrict__ proj, const float* __restrict__ conv_w,
@@ -43,16 +45,29 @@ delta_prepare_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __re
                      const float* __restrict__ A_log, const float* __restrict__ state,
                      const int* __restrict__ tok_req, const int* __restrict__ req_start,
                      const int* __restrict__ req_slot, DeltaShape s) {
-  extern __shared__ float s_c[];                 // [channels] after convolution and silu
+  extern __shared__ float s_c[];                 // [2 * kv_heads * D] q and k after conv and silu
   const int t = blockIdx.x;
   const int r = tok_req[t];
   if (r < 0) return;
   const int C = channels(s);
+  const int QK = s.kv_heads * s.D;
+  const float* row = proj + (size_t)t * s.stride;
+  if (blockIdx.y == 2) {
+    const int HD = s.heads * s.D;
+    for (int i = threadIdx.x; i < HD; i += blockDim.x) {
+      float z = 0.f;
+#pragma unroll 8
+      for (int k = 0; k < s.ra; ++k) z = fmaf(a2[(size_t)k * HD + i], row[s.a_off + k], z);
+      z += dt_bias[i];
+      decay[(size_t)t * HD + i] = expf(-expf(A_log[i / s.D]) * softplusf_(z));
+    }
+    return;
+  }
   const int first = req_start[r];
   const int l = t - first;
   const float* cst = state + (size_t)req_slot[r] * s.state_stride + (size_t)s.heads * s.D * s.V;
   const int hist = s.taps - 1;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+  auto conv = [&](int c) {
     float acc = 0.f;
 #pragma unroll 4
     for (int j = 0; j < s.taps; ++j) {
@@ -61,11 +76,18 @@ delta_prepare_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __re
                                   : cst[(size_t)(local + hist) * C + c];
       acc = fmaf(conv_w[(size_t)c * s.taps + j], in, acc);
     }
-    s_c[c] = acc * sigmoidf_(acc);
+    return acc * sigmoidf_(acc);
+  };
+  if (blockIdx.y == 1) {
+    const int HV = s.heads * s.V;
+    for (int i = threadIdx.x; i < HV; i += blockDim.x) vv[(size_t)t * HV + i] = conv(2 * QK + i);
+    for (int h = threadIdx.x; h < s.heads; h += blockDim.x)
+      beta[(size_t)t * s.heads + h] = sigmoidf_(row[s.b_off + h]);
+    return;
   }
+  for (int c = threadIdx.x; c < 2 * QK; c += blockDim.x) s_c[c] = conv(c);
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  const int QK = s.kv_heads * s.D;
   for (int vec = warp; vec < 2 * s.kv_heads; vec += nw) {       // q heads, then k heads
     const float* src = s_c + (size_t)vec * s.D;
     float ss = 0.f;
@@ -77,19 +99,6 @@ delta_prepare_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __re
     float* dst = is_q ? qn + (size_t)t * QK + (size_t)vec * s.D
                       : kn + (size_t)t * QK + (size_t)(vec - s.kv_heads) * s.D;
     for (int d = lane; d < s.D; d += 32) dst[d] = src[d] * inv;
-  }
-  const int HV = s.heads * s.V;
-  for (int i = threadIdx.x; i < HV; i += blockDim.x) vv[(size_t)t * HV + i] = s_c[2 * QK + i];
-  const float* row = proj + (size_t)t * s.stride;
-  for (int h = threadIdx.x; h < s.heads; h += blockDim.x)
-    beta[(size_t)t * s.heads + h] = sigmoidf_(row[s.b_off + h]);
-  const int HD = s.heads * s.D;
-  for (int i = threadIdx.x; i < HD; i += blockDim.x) {
-    float z = 0.f;
-#pragma unroll 8
-    for (int k = 0; k < s.ra; ++k) z = fmaf(a2[(size_t)k * HD + i], row[s.a_off + k], z);
-    z += dt_bias[i];
-    decay[(size_t)t * HD + i] = expf(-expf(A_log[i / s.D]) * softplusf_(z));
   }
 }
 
@@ -322,13 +331,13 @@ HS_EXPORT int hs_delta_prepare(float* qn, float* kn, float* vv, float* beta, flo
   if (rc) return rc;
   if (n_tokens <= 0 || n_requests <= 0) return HS_OK;
   const int C = 2 * kv_heads * D + heads * V;
-  const size_t smem = (size_t)C * sizeof(float);
+  const size_t smem = (size_t)2 * kv_heads * D * sizeof(float);
   if (smem > 200 * 1024) return HS_ERR_UNSUPPORTED;
   cudaStream_t st = (cudaStream_t)stream;
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(hs::delta_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          (int)smem);
-  hs::delta_prepare_kernel<<<n_tokens, 512, smem, st>>>(qn, kn, vv, beta, decay, proj, conv_w, a2,
+  hs::delta_prepare_kernel<<<dim3(n_tokens, 3), 256, smem, st>>>(qn, kn, vv, beta, decay, proj, conv_w, a2,
                                                         dt_bias, A_log, state, tok_req, req_start,
                                                         req_slot, s);
   HS_LAUNCH_CHECK();
