@@ -140,13 +140,61 @@ __device__ __forceinline__ float expert_act(float g, float u, float limit) {
 constexpr int GEMV_THREADS = 256;
 constexpr int GEMV_ROWS = 32;       // output rows a block covers
 
+// NS weight rows at once against one vector: the loads of all rows of a step over k are issued
+// before any is used, so that a lane has NS 16-byte loads in flight.  Rows whose pointer is null
+// give 0.  The per-row sum runs over k in the same order as row_dot's.
+template <int NS>
+__device__ __forceinline__ void rows_dot(float* res, const __nv_bfloat16* const* rows,
+                                         const float* v, int n, int lane) {
+  float acc[NS];
+#pragma unroll
+  for (int r = 0; r < NS; ++r) acc[r] = 0.f;
+  bool vec = (n & 7) == 0;
+#pragma unroll
+  for (int r = 0; r < NS; ++r) vec = vec && (((uintptr_t)rows[r]) & 15) == 0;
+  if (vec) {
+    for (int k = lane * 8; k < n; k += 256) {
+      uint4 raw[NS];
+#pragma unroll
+      for (int r = 0; r < NS; ++r)
+        raw[r] = rows[r] ? *(const uint4*)(rows[r] + k) : make_uint4(0, 0, 0, 0);
+      const float4 v0 = *(const float4*)(v + k), v1 = *(const float4*)(v + k + 4);
+#pragma unroll
+      for (int r = 0; r < NS; ++r) {
+        const __nv_bfloat162* p = (const __nv_bfloat162*)&raw[r];
+        float2 f = __bfloat1622float2(p[0]);
+        acc[r] = fmaf(f.x, v0.x, acc[r]); acc[r] = fmaf(f.y, v0.y, acc[r]);
+        f = __bfloat1622float2(p[1]);
+        acc[r] = fmaf(f.x, v0.z, acc[r]); acc[r] = fmaf(f.y, v0.w, acc[r]);
+        f = __bfloat1622float2(p[2]);
+        acc[r] = fmaf(f.x, v1.x, acc[r]); acc[r] = fmaf(f.y, v1.y, acc[r]);
+        f = __bfloat1622float2(p[3]);
+        acc[r] = fmaf(f.x, v1.z, acc[r]); acc[r] = fmaf(f.y, v1.w, acc[r]);
+      }
+    }
+  } else {
+    for (int k = lane; k < n; k += 32)
+#pragma unroll
+      for (int r = 0; r < NS; ++r)
+        if (rows[r]) acc[r] = fmaf(__bfloat162float(rows[r][k]), v[k], acc[r]);
+  }
+#pragma unroll
+  for (int r = 0; r < NS; ++r) res[r] = warp_sum(acc[r]);
+}
+template <int NS>
+__device__ __forceinline__ void rows_dot(float* res, const float* const* rows, const float* v,
+                                         int n, int lane) {
+#pragma unroll
+  for (int r = 0; r < NS; ++r) res[r] = rows[r] ? row_dot(rows[r], v, n, lane) : 0.f;
+}
+
 template <typename TW>
 __global__ void __launch_bounds__(GEMV_THREADS)
 moe_gate_up_rows_kernel(float* __restrict__ y, const TW* __restrict__ h,
                         const TW* __restrict__ w_gate, const TW* __restrict__ w_up,
                         const int* __restrict__ sel_idx, const int* __restrict__ tok_req,
                         int width, int ff, int top, int E, float limit) {
-  extern __shared__ float s_h[];                       // [width]
+  extern __shared__ __align__(16) float s_h[];         // [width]
   const int pair = blockIdx.x;
   const int t = pair / top;
   if (tok_req[t] < 0) return;
@@ -155,14 +203,26 @@ moe_gate_up_rows_kernel(float* __restrict__ y, const TW* __restrict__ h,
   for (int k = threadIdx.x; k < width; k += GEMV_THREADS) s_h[k] = to_f(h[(size_t)t * width + k]);
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int f_end = min(ff, (int)(blockIdx.y + 1) * GEMV_ROWS);
-  for (int f = blockIdx.y * GEMV_ROWS + warp; f < f_end; f += GEMV_THREADS / 32) {
+  constexpr int NW = GEMV_THREADS / 32, PER = GEMV_ROWS / NW;      // rows a warp: 4
+  const int f0 = blockIdx.y * GEMV_ROWS + warp;
+  const TW* rows[2 * PER];
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int f = f0 + i * NW;
     const size_t row = ((size_t)e * ff + f) * width;
-    const float g = row_dot(w_gate + row, s_h, width, lane);
-    const float u = row_dot(w_up + row, s_h, width, lane);
-    if (lane == 0) y[(size_t)pair * ff + f] = expert_act(g, u, limit);
+    rows[2 * i] = f < ff ? w_gate + row : nullptr;
+    rows[2 * i + 1] = f < ff ? w_up + row : nullptr;
+  }
+  float res[2 * PER];
+  rows_dot<2 * PER>(res, rows, s_h, width, lane);
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int f = f0 + i * NW;
+    if (lane == 0 && f < ff) y[(size_t)pair * ff + f] = expert_act(res[2 * i], res[2 * i + 1], limit);
   }
 }
+
+constexpr int MAX_TOP_AT_ONCE = 8;
 
 template <typename TW>
 __global__ void __launch_bounds__(GEMV_THREADS)
@@ -170,20 +230,65 @@ moe_down_rows_kernel(float* __restrict__ x, const float* __restrict__ y,
                      const TW* __restrict__ w_down, const int* __restrict__ sel_idx,
                      const float* __restrict__ sel_w, const int* __restrict__ tok_req, int width,
                      int ff, int top, int E) {
-  extern __shared__ float s_y[];                       // [top][ff]
+  extern __shared__ __align__(16) float s_y[];         // [top][ff4]: rows padded to 16 bytes
   const int t = blockIdx.x;
   if (tok_req[t] < 0) return;
-  for (int i = threadIdx.x; i < top * ff; i += GEMV_THREADS) s_y[i] = y[(size_t)t * top * ff + i];
+  const int ff4 = (ff + 3) & ~3;
+  for (int i = threadIdx.x; i < top * ff4; i += GEMV_THREADS) {
+    const int k = i / ff4, f = i - k * ff4;
+    s_y[i] = f < ff ? y[((size_t)t * top + k) * ff + f] : 0.f;
+  }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_end = min(width, (int)(blockIdx.y + 1) * GEMV_ROWS);
   for (int n = blockIdx.y * GEMV_ROWS + warp; n < n_end; n += GEMV_THREADS / 32) {
     float sum = 0.f;
-    for (int k = 0; k < top; ++k) {
-      const int e = sel_idx[(size_t)t * top + k];
-      if (e < 0 || e >= E) continue;
-      const float acc = row_dot(w_down + ((size_t)e * width + n) * ff, s_y + (size_t)k * ff, ff, lane);
-      sum = fmaf(sel_w[(size_t)t * top + k], acc, sum);
+    for (int k0 = 0; k0 < top; k0 += MAX_TOP_AT_ONCE) {
+      // the rows of up to eight chosen experts for this output, fetched together; each is
+      // summed against its own activations, then weighted, in the order of the choice
+      float acc[MAX_TOP_AT_ONCE];
+      if (sizeof(TW) == 2 && (ff & 7) == 0) {
+        const TW* rows[MAX_TOP_AT_ONCE];
+#pragma unroll
+        for (int i = 0; i < MAX_TOP_AT_ONCE; ++i) {
+          const int e = k0 + i < top ? sel_idx[(size_t)t * top + k0 + i] : -1;
+          rows[i] = (e >= 0 && e < E) ? w_down + ((size_t)e * width + n) * ff : nullptr;
+          acc[i] = 0.f;
+        }
+        for (int k = lane * 8; k < ff; k += 256) {
+          uint4 raw[MAX_TOP_AT_ONCE];
+#pragma unroll
+          for (int i = 0; i < MAX_TOP_AT_ONCE; ++i)
+            raw[i] = rows[i] ? *(const uint4*)((const __nv_bfloat16*)rows[i] + k)
+                             : make_uint4(0, 0, 0, 0);
+#pragma unroll
+          for (int i = 0; i < MAX_TOP_AT_ONCE; ++i) {
+            if (!rows[i]) continue;
+            const float* v = s_y + (size_t)(k0 + i) * ff4 + k;
+            const __nv_bfloat162* p = (const __nv_bfloat162*)&raw[i];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float2 f = __bfloat1622float2(p[q]);
+              acc[i] = fmaf(f.x, v[2 * q], acc[i]);
+              acc[i] = fmaf(f.y, v[2 * q + 1], acc[i]);
+            }
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < MAX_TOP_AT_ONCE; ++i) acc[i] = warp_sum(acc[i]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < MAX_TOP_AT_ONCE; ++i) {
+          const int e = k0 + i < top ? sel_idx[(size_t)t * top + k0 + i] : -1;
+          acc[i] = (e >= 0 && e < E)
+                       ? row_dot(w_down + ((size_t)e * width + n) * ff,
+                                 s_y + (size_t)(k0 + i) * ff4, ff, lane)
+                       : 0.f;
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < MAX_TOP_AT_ONCE; ++i)
+        if (k0 + i < top) sum = fmaf(sel_w[(size_t)t * top + k0 + i], acc[i], sum);
     }
     if (lane == 0) x[(size_t)t * width + n] += sum;
   }
@@ -470,7 +575,7 @@ HS_EXPORT int hs_moe_experts(float* x, float* y, const void* h, const void* w_ga
   }
   if (!y) return HS_ERR_ARGUMENT;
   const size_t smem_h = (size_t)width * sizeof(float);
-  const size_t smem_y = (size_t)top * ff * sizeof(float);
+  const size_t smem_y = (size_t)top * ((ff + 3) & ~3) * sizeof(float);
   if (smem_h > 200 * 1024 || smem_y > 200 * 1024) return HS_ERR_UNSUPPORTED;
   dim3 g1(n_tokens * top, (ff + hs::GEMV_ROWS - 1) / hs::GEMV_ROWS);
   dim3 g2(n_tokens, (width + hs::GEMV_ROWS - 1) / hs::GEMV_ROWS);
