@@ -14,10 +14,12 @@
 // Pool rows: [pages, page_size, R + P] in the cache type; row of position p of request r is
 // table[r, p / page_size] * page_size + p % page_size.
 #include "common.cuh"
+#include "rotary.cuh"
 
 namespace hs {
 
-// -- append: RMS-norm the latent, copy the (already rotated) key part, write the cache row ------
+// -- append: RMS-norm the latent, rotate the key part (the first rot_dims entries; 0: it arrives
+//    rotated), write the cache row -----------------------------------------------------------------
 template <typename TC>
 __global__ void latent_append_kernel(TC* __restrict__ pool, const float* __restrict__ proj,
                                      const float* __restrict__ norm_w,
@@ -25,7 +27,8 @@ __global__ void latent_append_kernel(TC* __restrict__ pool, const float* __restr
                                      const int* __restrict__ tok_pos,
                                      const int* __restrict__ tok_req, int proj_stride, int c_off,
                                      int R, int P, float eps, int page_size, int num_pages,
-                                     int max_pages, int* status) {
+                                     int max_pages, int* status,
+                                     const float* __restrict__ freq, int rot_dims) {
   __shared__ float red[4];
   __shared__ float bcast;
   const int t = blockIdx.x;
@@ -53,7 +56,9 @@ __global__ void latent_append_kernel(TC* __restrict__ pool, const float* __restr
   const float rs = bcast;
   TC* dst = pool + ((size_t)page * page_size + (p % page_size)) * (R + P);
   for (int e = threadIdx.x; e < R; e += blockDim.x) dst[e] = from_f<TC>(src[e] * rs * norm_w[e]);
-  for (int e = threadIdx.x; e < P; e += blockDim.x) dst[R + e] = from_f<TC>(src[R + e]);
+  for (int e = threadIdx.x; e < P; e += blockDim.x)
+    dst[R + e] = from_f<TC>(e < rot_dims ? rotate_entry(src[R + e], src[R + (e ^ 1)], e, rot_dims, p, freq)
+                                         : src[R + e]);
 }
 
 // -- attention ---------------------------------------------------------------------------------
@@ -75,7 +80,8 @@ latent_attention_kernel(float* __restrict__ out, const float* __restrict__ qa,
                         const int* __restrict__ tok_req, const float* __restrict__ sink,
                         int n_heads, int R, int P, int qr_stride, int qr_hstride, int qr_off,
                         float scale, int page_size, int num_pages, int max_pages, int* status,
-                        int nsplit, float* __restrict__ partial) {
+                        int nsplit, float* __restrict__ partial,
+                        const float* __restrict__ freq, int rot_dims) {
   extern __shared__ __align__(16) float smem[];
   const int W = R + P;
   const int W4 = la_w4(W), ks = la_stride(W);
@@ -93,9 +99,15 @@ latent_attention_kernel(float* __restrict__ out, const float* __restrict__ qa,
     const int hh = i / W4, d = i - hh * W4;
     const int head = blockIdx.y * LA_HB + hh;
     float v = 0.f;
-    if (head < n_heads && d < W)
-      v = d < R ? qa[((size_t)t * n_heads + head) * R + d]
-                : qr[(size_t)t * qr_stride + (size_t)head * qr_hstride + qr_off + (d - R)];
+    if (head < n_heads && d < W) {
+      if (d < R) {
+        v = qa[((size_t)t * n_heads + head) * R + d];
+      } else {                      // the rotated part: turned here when it arrives unrotated
+        const float* src = qr + (size_t)t * qr_stride + (size_t)head * qr_hstride + qr_off;
+        const int e = d - R;
+        v = e < rot_dims ? rotate_entry(src[e], src[e ^ 1], e, rot_dims, pos, freq) : src[e];
+      }
+    }
     s_q[i] = v;
   }
   // alone, a block opens its running softmax with the sink (weight 1); as one of `nsplit`
@@ -210,7 +222,8 @@ HS_EXPORT int hs_latent_append(void* pool, const float* proj, const float* norm_
                                const int* table, const int* tok_pos, const int* tok_req,
                                int n_tokens, int proj_stride, int c_off, int R, int P, float eps,
                                int page_size, int num_pages, int max_pages, int cache_dtype,
-                               int* status, void* stream) {
+                               int* status, const float* freq, int rot_dims, void* stream) {
+  if (rot_dims < 0 || rot_dims % 2 || rot_dims > P || (rot_dims && !freq)) return HS_ERR_ARGUMENT;
   if (!pool || !proj || !norm_w || !table || !tok_pos || !tok_req || !status)
     return HS_ERR_ARGUMENT;
   if (R <= 0 || P < 0 || page_size <= 0) return HS_ERR_UNSUPPORTED;
@@ -219,11 +232,11 @@ HS_EXPORT int hs_latent_append(void* pool, const float* proj, const float* norm_
   if (cache_dtype == HS_DT_F32)
     hs::latent_append_kernel<float><<<n_tokens, 128, 0, st>>>(
         (float*)pool, proj, norm_w, table, tok_pos, tok_req, proj_stride, c_off, R, P, eps,
-        page_size, num_pages, max_pages, status);
+        page_size, num_pages, max_pages, status, freq, rot_dims);
   else if (cache_dtype == HS_DT_BF16)
     hs::latent_append_kernel<__nv_bfloat16><<<n_tokens, 128, 0, st>>>(
         (__nv_bfloat16*)pool, proj, norm_w, table, tok_pos, tok_req, proj_stride, c_off, R, P,
-        eps, page_size, num_pages, max_pages, status);
+        eps, page_size, num_pages, max_pages, status, freq, rot_dims);
   else
     return HS_ERR_UNSUPPORTED;
   HS_LAUNCH_CHECK();
@@ -236,7 +249,8 @@ static int launch_latent_attention(float* out, const float* qa, const float* qr,
                                    const float* sink, int n_tokens, int n_heads, int R, int P,
                                    int qr_stride, int qr_hstride, int qr_off, float scale,
                                    int page_size, int num_pages, int max_pages, int* status,
-                                   int nsplit, float* partial, cudaStream_t st) {
+                                   int nsplit, float* partial, const float* freq, int rot_dims,
+                                   cudaStream_t st) {
   const int W = R + P;
   const size_t smem = ((size_t)hs::LA_HB * hs::la_w4(W) + (size_t)hs::LA_TILE * hs::la_stride(W)) *
                       sizeof(float);
@@ -248,7 +262,7 @@ static int launch_latent_attention(float* out, const float* qa, const float* qr,
   kern<<<grid, hs::LA_HB * 32, smem, st>>>(out, qa, qr, (const TC*)pool, table, tok_pos, tok_req,
                                            sink, n_heads, R, P, qr_stride, qr_hstride, qr_off,
                                            scale, page_size, num_pages, max_pages, status, nsplit,
-                                           partial);
+                                           partial, freq, rot_dims);
   HS_LAUNCH_CHECK();
   if (nsplit > 1) {
     hs::latent_merge_kernel<<<dim3(n_tokens, n_heads), 128, 0, st>>>(out, partial, sink, tok_req,
@@ -263,8 +277,10 @@ HS_EXPORT int hs_latent_attention(float* out, const float* qa, const float* qr, 
                                   const float* sink, int n_tokens, int n_heads, int R, int P,
                                   int qr_stride, int qr_hstride, int qr_off, float scale,
                                   int page_size, int num_pages, int max_pages, int cache_dtype,
-                                  int* status, int nsplit, float* partial, void* stream) {
+                                  int* status, int nsplit, float* partial, const float* freq,
+                                  int rot_dims, void* stream) {
   if (nsplit < 1 || (nsplit > 1 && !partial)) return HS_ERR_ARGUMENT;
+  if (rot_dims < 0 || rot_dims % 2 || rot_dims > P || (rot_dims && !freq)) return HS_ERR_ARGUMENT;
   if (!out || !qa || !qr || !pool || !table || !tok_pos || !tok_req || !sink || !status)
     return HS_ERR_ARGUMENT;
   if (R <= 0 || R > 512 || P < 0 || n_heads <= 0 || page_size <= 0) return HS_ERR_UNSUPPORTED;
@@ -275,7 +291,7 @@ HS_EXPORT int hs_latent_attention(float* out, const float* qa, const float* qr, 
   return launch_latent_attention<TC, RC>(out, qa, qr, pool, table, tok_pos, tok_req, sink,    \
                                          n_tokens, n_heads, R, P, qr_stride, qr_hstride,      \
                                          qr_off, scale, page_size, num_pages, max_pages,      \
-                                         status, nsplit, partial, st)
+                                         status, nsplit, partial, freq, rot_dims, st)
 #define HS_LA_RC(TC)                   \
   do {                                 \
     if (rc <= 4) HS_LA(TC, 4);         \

@@ -7,6 +7,7 @@
 //            The table f (dims/2 floats) comes from the host, formed in double.  The angle is
 //            formed in double and reduced there, so that its error does not grow with p.
 #include "common.cuh"
+#include "rotary.cuh"
 
 namespace hs {
 
@@ -26,13 +27,6 @@ __global__ void scale_kernel(float* __restrict__ t, long long n, float s) {
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long step = (long long)gridDim.x * blockDim.x;
   for (; i < n; i += step) t[i] = t[i] * s;
-}
-
-__device__ __forceinline__ void pair_angle(int p, float f, float* c, float* s) {
-  const double two_pi = 6.283185307179586476925286766559;
-  double a = (double)p * (double)f;
-  a -= two_pi * floor(a / two_pi);
-  sincosf((float)a, s, c);
 }
 
 // One block per token row; `n_vec` vectors at columns offset + v * vec_stride.

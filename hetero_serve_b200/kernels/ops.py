@@ -187,9 +187,9 @@ def _declare(lib) -> None:
         "hs_scale": [P, ctypes.c_longlong, F, P],
         "hs_rotary_pairs": [P, P, P, P, I, I, I, I, I, I, P],
         "hs_grouped_linear": [P, P, P, I, I, I, I, I, I, I, I, I, P],
-        "hs_latent_append": [P, P, P, P, P, P, I, I, I, I, I, F, I, I, I, I, P, P],
+        "hs_latent_append": [P, P, P, P, P, P, I, I, I, I, I, F, I, I, I, I, P, P, I, P],
         "hs_latent_attention": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, I, I, P, I,
-                                P, P],
+                                P, P, I, P],
         "hs_delta_prepare": [P] * 15 + [I] * 9 + [P],
         "hs_delta_recurrence": [P] * 10 + [I] * 8 + [P],
         "hs_delta_finish": [P, P, P, P, P, P, I, F, I, I, I, I, I, I, I, I, P],
@@ -1007,10 +1007,12 @@ class CudaOps:
 
     # -- attention over a shared latent ---------------------------------------------------
     def latent_append(self, pool, proj, norm_w, table, tok_pos, tok_req, *, c_offset, rank,
-                      rot_dim, eps, page_size, status):
+                      rot_dim, eps, page_size, status, freq=None, rot_dims=0):
         """Cache row of each token: ``[rms_norm(proj[t, c_offset : +rank]) * norm_w |
-        proj[t, c_offset + rank : + rot_dim]]`` (the second part as it stands: rotate it
-        before).  ``pool`` is [pages, 1, 1, page_size, rank + rot_dim]."""
+        proj[t, c_offset + rank : + rot_dim]]``; with ``freq`` the first ``rot_dims`` entries
+        of the second part are rotated on the way (interleaved pairs, as ``rotary_pairs``),
+        without it the part is taken as it stands.  ``pool`` is [pages, 1, 1, page_size,
+        rank + rot_dim]."""
         _want(proj, "proj", torch.float32, 2)
         _want(pool, "pool", _FLOATS)
         _want(norm_w, "norm_w", torch.float32, 1)
@@ -1026,16 +1028,20 @@ class CudaOps:
                                          _ptr(tok_pos), _ptr(tok_req), n, proj.shape[1],
                                          int(c_offset), rank, rot_dim, float(eps), page_size,
                                          pool.numel() // (page_size * W), table.shape[1],
-                                         _DT[pool.dtype], _ptr(status), self._stream()),
+                                         _DT[pool.dtype], _ptr(status), _ptr(freq),
+                                         int(rot_dims) if freq is not None else 0,
+                                         self._stream()),
                "latent_append")
 
     def latent_attention(self, out, qa, qr, pool, table, tok_pos, tok_req, sink, *, n_heads,
-                         rank, rot_dim, qr_head_stride, qr_offset, scale, page_size, status):
+                         rank, rot_dim, qr_head_stride, qr_offset, scale, page_size, status,
+                         freq=None, rot_dims=0):
         """Causal softmax attention with a sink over cache rows ``[c (rank) | kr (rot_dim)]``
         shared by all heads: score = (qa[t,h] . c + qr[t,h] . kr) * scale, the denominator
         also holds exp(sink[h]); ``out[t, h] = sum_j weight_j c_j`` ([T, n_heads * rank],
         float32).  ``qa`` [T, n_heads * rank] float32; head h's rotated query part is
-        ``qr[t, qr_offset + h * qr_head_stride : + rot_dim]``."""
+        ``qr[t, qr_offset + h * qr_head_stride : + rot_dim]``; with ``freq`` it arrives
+        unrotated and its first ``rot_dims`` entries are rotated as they are read."""
         _want(out, "out", torch.float32, 2)
         _want(qa, "qa", torch.float32, 2)
         _want(qr, "qr", torch.float32, 2)
@@ -1064,8 +1070,8 @@ class CudaOps:
             _ptr(out), _ptr(qa), _ptr(qr), _ptr(pool), _ptr(table), _ptr(tok_pos), _ptr(tok_req),
             _ptr(sink), n, n_heads, rank, rot_dim, qr.shape[1], int(qr_head_stride),
             int(qr_offset), float(scale), page_size, pool.numel() // (page_size * W),
-            table.shape[1], _DT[pool.dtype], _ptr(status), nsplit, _ptr(partial),
-            self._stream()),
+            table.shape[1], _DT[pool.dtype], _ptr(status), nsplit, _ptr(partial), _ptr(freq),
+            int(rot_dims) if freq is not None else 0, self._stream()),
             f"latent_attention(rank={rank},rot_dim={rot_dim})")
 
     # -- the gated delta rule ---------------------------------------------------------------

@@ -79,25 +79,22 @@ class LatentAttention(Mixer):
         H, D, P, V, R = self.H, self.D, self.P, self.V, self.R
         proj = ctx.buffer("latent_proj", (T, self.in_width), torch.float32)
         ops.linear(proj, h, self.w_in)
-        if self.rot_dims:
-            ops.rotary_pairs(proj, ctx.tok_pos, ctx.tok_req, self.freq, n_vec=H,
-                             vec_stride=D + P, offset=D, dims=self.rot_dims)
+        # both rotations are fused: the key part turns as it is written to the page, the query
+        # parts as the attention kernel reads them
+        rot = dict(freq=self.freq, rot_dims=self.rot_dims) if self.rot_dims else {}
         if cache.writes:
             if self.shares_cache:
                 raise RuntimeError("a layer that shares a latent cache cannot write it")
-            if self.rot_dims:
-                ops.rotary_pairs(proj, ctx.tok_pos, ctx.tok_req, self.freq, n_vec=1,
-                                 vec_stride=P, offset=self.q_width + R, dims=self.rot_dims)
             ops.latent_append(cache.pool, proj, self.norm_w, cache.table, ctx.tok_pos,
                               ctx.tok_req, c_offset=self.q_width, rank=R, rot_dim=P,
-                              eps=self.eps, page_size=cache.page_size, status=ctx.status)
+                              eps=self.eps, page_size=cache.page_size, status=ctx.status, **rot)
         qa = ctx.buffer("latent_qa", (T, H * R), torch.float32)
         ops.grouped_linear(qa, proj, self.w_absorb, a_offset=0, a_group_stride=D + P)
         lat = ctx.buffer("latent_mix", (T, H * R), torch.float32)
         ops.latent_attention(lat, qa, proj, cache.pool, cache.table, ctx.tok_pos, ctx.tok_req,
                              self.sink, n_heads=H, rank=R, rot_dim=P, qr_head_stride=D + P,
                              qr_offset=D, scale=self.scale, page_size=cache.page_size,
-                             status=ctx.status)
+                             status=ctx.status, **rot)
         att = ctx.buffer("latent_heads", (T, H * V), ctx.dtype)
         ops.grouped_linear(att, lat, self.w_expand)
         ops.linear(x, att, self.w_out, None, residual=x)

@@ -100,3 +100,9 @@ def pedorax_cases(tmp_path_factory):
 @pytest.fixture(params=["case_a", "case_b"])
 def pedorax_case(request, pedorax_cases):
     return pedorax_cases[request.param]
+
+
+@pytest.fixture(params=["case_c", "case_d"])
+def pedorax_one_kind(request, pedorax_cases):
+    """Models with layers of one kind only: no page group at all, or no state in use."""
+    return pedorax_cases[request.param]

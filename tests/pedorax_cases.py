@@ -62,7 +62,28 @@ CASE_B = {
     ],
 }
 
-CASES = {"case_a": (CASE_A, 11), "case_b": (CASE_B, 12)}
+# only recurrent layers (no page group at all), and only attention layers (no state slot in use)
+CASE_C = {
+    "architecture": "Pedorax", "vocab": 50, "width": 24, "embedding": {"scale": 0.5},
+    "logit_scale": -2.0, "norm": {"eps": 1e-5},
+    "layers": [
+        {"type": "channel_delta", "mixer": _delta(2, 1, 8, 12, 4, 3, 3), "mlp": None},
+        {"type": "channel_delta", "mixer": _delta(3, 3, 4, 4, 2, 2, 5), "mlp": _moe(8, 2, 2, 2, 2, 1.0)},
+    ],
+}
+CASE_D = {
+    "architecture": "Pedorax", "vocab": 61, "width": 28, "embedding": {"scale": 1.25},
+    "logit_scale": 0.5, "norm": {"eps": 1e-5},
+    "layers": [
+        {"type": "latent_attention", "mixer": _latent(2, 4, 6, 10, 9, 100.0, 0, 0.5), "mlp": None},
+        {"type": "latent_attention", "mixer": _latent(3, 6, 6, 4, 9, 100.0, 0, 0.4, kv_from=0),
+         "mlp": _moe(10, 3, 1, 3, 2, 2.0)},
+        {"type": "latent_attention", "mixer": _latent(1, 6, 2, 4, 7, 9.0, 2, 0.4), "mlp": None},
+    ],
+}
+
+CASES = {"case_a": (CASE_A, 11), "case_b": (CASE_B, 12), "case_c": (CASE_C, 13),
+         "case_d": (CASE_D, 14)}
 
 
 class Case:

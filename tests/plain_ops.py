@@ -162,8 +162,20 @@ class PlainOps:
             v = a[:T, lo:lo + k].to(self.cd) @ w[g].to(self.cd)
             out[:, g * n:(g + 1) * n] = v.to(out.dtype)
 
+    def _turned(self, vec, position, freq, rot_dims):
+        """vec with the interleaved pairs of its first rot_dims entries rotated (a copy)."""
+        out = vec.to(self.cd).clone()
+        if freq is None or not rot_dims:
+            return out
+        ang = float(position) * freq[:rot_dims // 2].to(self.cd)
+        c, s = torch.cos(ang), torch.sin(ang)
+        a, b = out[0:rot_dims:2].clone(), out[1:rot_dims:2].clone()
+        out[0:rot_dims:2] = a * c - b * s
+        out[1:rot_dims:2] = b * c + a * s
+        return out
+
     def latent_append(self, pool, proj, norm_w, table, tok_pos, tok_req, *, c_offset, rank,
-                      rot_dim, eps, page_size, status):
+                      rot_dim, eps, page_size, status, freq=None, rot_dims=0):
         rows = pool.view(-1, page_size, rank + rot_dim)
         for t in range(proj.shape[0]):
             r = int(tok_req[t])
@@ -174,11 +186,12 @@ class PlainOps:
             c = proj[t, c_offset:c_offset + rank].to(self.cd)
             c = c / torch.sqrt((c * c).mean() + eps) * norm_w.to(self.cd)
             rows[page, p % page_size, :rank] = c.to(pool.dtype)
-            rows[page, p % page_size, rank:] = proj[t, c_offset + rank:c_offset + rank + rot_dim
-                                                    ].to(pool.dtype)
+            kr = self._turned(proj[t, c_offset + rank:c_offset + rank + rot_dim], p, freq, rot_dims)
+            rows[page, p % page_size, rank:] = kr.to(pool.dtype)
 
     def latent_attention(self, out, qa, qr, pool, table, tok_pos, tok_req, sink, *, n_heads,
-                         rank, rot_dim, qr_head_stride, qr_offset, scale, page_size, status):
+                         rank, rot_dim, qr_head_stride, qr_offset, scale, page_size, status,
+                         freq=None, rot_dims=0):
         rows = pool.view(-1, page_size, rank + rot_dim)
         scale32 = float(torch.tensor(scale, dtype=torch.float32))
         for t in range(out.shape[0]):
@@ -193,7 +206,7 @@ class PlainOps:
             for h in range(n_heads):
                 qh = qa[t, h * rank:(h + 1) * rank].to(self.cd)
                 lo = qr_offset + h * qr_head_stride
-                s = (c @ qh + kr @ qr[t, lo:lo + rot_dim].to(self.cd)) * scale32
+                s = (c @ qh + kr @ self._turned(qr[t, lo:lo + rot_dim], p, freq, rot_dims)) * scale32
                 top = torch.maximum(s.max(), sink[h].to(self.cd))
                 e = torch.exp(s - top)
                 den = e.sum() + torch.exp(sink[h].to(self.cd) - top)

@@ -170,3 +170,14 @@ def test_a_slot_is_cleared_for_its_next_owner(pedorax_cases):
     res = rn.step([StepEntry("b", b[10:], want=[6])])
     assert (res.logits[0].double() - case.logits(b)[16]).abs().max() < TOL
     rn.manager.check()
+
+
+def test_models_with_layers_of_one_kind(pedorax_one_kind, tmp_path):
+    """Only recurrent layers (the cache has no page group), or only attention layers (no state;
+    no rotation at all in two of them, a negative logit scale in the other model)."""
+    case = pedorax_one_kind
+    reqs = {f"r{i}": case.tokens(n, 90 + i) for i, n in enumerate((21, 40, 3))}
+    steps, index, peak = traces.mixed(reqs, seed=5, max_live=2, sizes=(1, 2, 7, 1, 17, 3))
+    out = _replay(case, steps, tmp_path, max_tokens=peak, max_requests=2)
+    err, where = _worst(case, out, index, reqs)
+    assert err < TOL, (err, where)

@@ -71,6 +71,16 @@ def test_mixed_batches_reuse_pages_and_slots(pedorax_case, tmp_path, dtype):
     assert n > 40 and err < TOL[dtype], (err, where)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_models_with_layers_of_one_kind(pedorax_one_kind, tmp_path, dtype):
+    case = pedorax_one_kind
+    reqs = {f"r{i}": case.tokens(n, 190 + i) for i, n in enumerate((60, 41, 3, 100))}
+    steps, index, peak = traces.mixed(reqs, seed=6, max_live=3)
+    out = _replay(case, dtype, steps, tmp_path, max_tokens=peak, max_requests=3)
+    err, where, n = _worst(case, dtype, out, index, reqs)
+    assert n > 10 and err < TOL[dtype], (err, where)
+
+
 def _runner(case, dtype="float32", pages=16, slots=4, **kw):
     model, _ = load_model(case.dir, dtype, DEV)
     return Runner(model, num_pages=pages, page_size=16, max_requests=slots, dtype=model.dtype,

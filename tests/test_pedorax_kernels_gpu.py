@@ -212,6 +212,49 @@ def test_latent_attention_finds_one_key_among_hundreds(ops, plain, where):
         assert (got2[0].cpu().double() - key[:16].double()).abs().max() > 0.3
 
 
+def test_latent_rotations_fused_into_append_and_attention(ops, plain):
+    """The key part turns as it is written, the query parts as they are read: the same as
+    rotating both beforehand with rotary_pairs."""
+    rank, rot, heads, dims = 24, 12, 3, 8
+    lens = (45, 20)
+    freq = torch.pow(torch.tensor(300.0, dtype=torch.float64), -2.0 * torch.arange(dims // 2) / dims)
+    f32 = freq.float()
+    lat = Latent(ops, plain, lens, rank, rot, F32, seed=44)
+    pos = torch.cat([torch.arange(n) for n in lens]).to(I32)
+    req = torch.cat([torch.full((n,), r) for r, n in enumerate(lens)]).to(I32)
+    proj = rnd(len(pos), 3 + rank + rot, seed=45)
+    norm_w = rnd(rank, seed=46).abs() + 0.5
+    # expected: rotate first with the twin of rotary_pairs, then the plain append
+    turned = proj.double().clone()
+    plain.rotary_pairs(turned, pos, req, freq, n_vec=1, vec_stride=rot, offset=3 + rank, dims=dims)
+    want_pool = torch.zeros_like(lat.pool, dtype=torch.float64)
+    plain.latent_append(want_pool, turned, norm_w, lat.table, pos, req, c_offset=3, rank=rank,
+                        rot_dim=rot, eps=1e-5, page_size=16, status=None)
+    status = torch.zeros(1, dtype=I32, device=DEV)
+    ops.latent_append(lat.pool_dev, dev(proj), dev(norm_w), dev(lat.table), dev(pos), dev(req),
+                      c_offset=3, rank=rank, rot_dim=rot, eps=1e-5, page_size=16, status=status,
+                      freq=dev(f32), rot_dims=dims)
+    close(lat.pool_dev, want_pool, 3e-6)
+    lat.pool = lat.pool_dev.cpu().clone()
+    n = 4
+    qpos, qreq = ints(44, 7, 19, 0), ints(0, 0, 1, 1)
+    qa, qr = rnd(n, heads * rank, seed=47, std=0.3), rnd(n, 2 + heads * (rot + 5), seed=48, std=0.3)
+    qr_turned = qr.double().clone()
+    plain.rotary_pairs(qr_turned, qpos, qreq, freq, n_vec=heads, vec_stride=rot + 5, offset=2, dims=dims)
+    sink = rnd(heads, seed=49)
+    want = torch.zeros(n, heads * rank, dtype=torch.float64)
+    plain.latent_attention(want, qa, qr_turned, lat.pool, lat.table, qpos, qreq, sink,
+                           n_heads=heads, rank=rank, rot_dim=rot, qr_head_stride=rot + 5,
+                           qr_offset=2, scale=0.3, page_size=16, status=None)
+    got = torch.zeros(n, heads * rank, dtype=F32, device=DEV)
+    ops.latent_attention(got, dev(qa), dev(qr), lat.pool_dev, dev(lat.table), dev(qpos), dev(qreq),
+                         dev(sink), n_heads=heads, rank=rank, rot_dim=rot, qr_head_stride=rot + 5,
+                         qr_offset=2, scale=0.3, page_size=16, status=status, freq=dev(f32),
+                         rot_dims=dims)
+    close(got, want, 2e-5)
+    assert int(status.item()) == 0
+
+
 def test_latent_attention_sink_takes_weight_without_a_value(ops, plain):
     lat = _fill(ops, plain, (40,), 24, 8, F32, seed=40)
     queries = [(0, 0), (0, 39)]
