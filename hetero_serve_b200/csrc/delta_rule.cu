@@ -226,36 +226,66 @@ delta_recurrence_kernel(float* __restrict__ o, float* __restrict__ state,
     const float* b_g = b_q + CH * Dp;
     const float* b_v = b_g + CH * Dp;
     const float* b_b = b_v + CH * cols;
-    for (int tt = 0; tt < nc; ++tt) {
+    // Two register sets alternate: while a token is worked on, the rows of the next one are
+    // already on their way from shared memory.  The sum over a column's lanes for a token's
+    // output (needed only by the store) rides along with the next token's sum for its dot
+    // product, stage by stage, so the chain from token to token holds one butterfly, not two.
+    struct Rows { float k[DR_DP], q[DR_DP], g[DR_DP], v, b; };
+    auto read = [&](int tt, Rows& r) {
       const float4* k4 = (const float4*)(b_k + tt * Dp + d0);
       const float4* q4 = (const float4*)(b_q + tt * Dp + d0);
       const float4* g4 = (const float4*)(b_g + tt * Dp + d0);
-      float kk[DR_DP], qq[DR_DP];
-      float dot0 = 0.f, dot1 = 0.f;
 #pragma unroll
       for (int j = 0; j < DR_DP / 4; ++j) {
         const float4 a = k4[j * KS], b = q4[j * KS], c = g4[j * KS];
-        kk[4 * j] = a.x; kk[4 * j + 1] = a.y; kk[4 * j + 2] = a.z; kk[4 * j + 3] = a.w;
-        qq[4 * j] = b.x; qq[4 * j + 1] = b.y; qq[4 * j + 2] = b.z; qq[4 * j + 3] = b.w;
-        st[4 * j] *= c.x; st[4 * j + 1] *= c.y; st[4 * j + 2] *= c.z; st[4 * j + 3] *= c.w;
-        dot0 = fmaf(st[4 * j], a.x, dot0); dot1 = fmaf(st[4 * j + 1], a.y, dot1);
-        dot0 = fmaf(st[4 * j + 2], a.z, dot0); dot1 = fmaf(st[4 * j + 3], a.w, dot1);
+        r.k[4 * j] = a.x; r.k[4 * j + 1] = a.y; r.k[4 * j + 2] = a.z; r.k[4 * j + 3] = a.w;
+        r.q[4 * j] = b.x; r.q[4 * j + 1] = b.y; r.q[4 * j + 2] = b.z; r.q[4 * j + 3] = b.w;
+        r.g[4 * j] = c.x; r.g[4 * j + 1] = c.y; r.g[4 * j + 2] = c.z; r.g[4 * j + 3] = c.w;
+      }
+      r.v = b_v[tt * cols + lc];
+      r.b = b_b[tt];
+    };
+    float pend = 0.f;               // the token before: its output, not yet summed over the lanes
+    int pend_tt = -1;
+    auto work = [&](int tt, const Rows& r, Rows& next) {
+      if (tt + 1 < nc) read(tt + 1, next);
+      float dot0 = 0.f, dot1 = 0.f;
+#pragma unroll
+      for (int j = 0; j < DR_DP; j += 2) {
+        st[j] *= r.g[j];
+        st[j + 1] *= r.g[j + 1];
+        dot0 = fmaf(st[j], r.k[j], dot0);
+        dot1 = fmaf(st[j + 1], r.k[j + 1], dot1);
       }
       float dot = dot0 + dot1;
-      for (int off = 1; off < KS; off <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
-      const float u = b_b[tt] * (b_v[tt * cols + lc] - dot);
+      for (int off = 1; off < KS; off <<= 1) {
+        const float d2 = __shfl_xor_sync(0xffffffffu, dot, off);
+        const float p2 = __shfl_xor_sync(0xffffffffu, pend, off);
+        dot += d2;
+        pend += p2;
+      }
+      if (pend_tt >= 0 && part == 0 && col_ok)
+        o[(size_t)(first + c0 + pend_tt) * HV + h * s.V + col] = pend;
+      const float u = r.b * (r.v - dot);
       float out0 = 0.f, out1 = 0.f;
 #pragma unroll
       for (int j = 0; j < DR_DP; j += 2) {
-        st[j] = fmaf(kk[j], u, st[j]);
-        st[j + 1] = fmaf(kk[j + 1], u, st[j + 1]);
-        out0 = fmaf(st[j], qq[j], out0);
-        out1 = fmaf(st[j + 1], qq[j + 1], out1);
+        st[j] = fmaf(r.k[j], u, st[j]);
+        st[j + 1] = fmaf(r.k[j + 1], u, st[j + 1]);
+        out0 = fmaf(st[j], r.q[j], out0);
+        out1 = fmaf(st[j + 1], r.q[j + 1], out1);
       }
-      float out = out0 + out1;
-      for (int off = 1; off < KS; off <<= 1) out += __shfl_xor_sync(0xffffffffu, out, off);
-      if (part == 0 && col_ok) o[(size_t)(first + c0 + tt) * HV + h * s.V + col] = out;
+      pend = out0 + out1;
+      pend_tt = tt;
+    };
+    Rows ra, rb;
+    read(0, ra);
+    for (int tt = 0; tt < nc; tt += 2) {
+      work(tt, ra, rb);
+      if (tt + 1 < nc) work(tt + 1, rb, ra);
     }
+    for (int off = 1; off < KS; off <<= 1) pend += __shfl_xor_sync(0xffffffffu, pend, off);
+    if (part == 0 && col_ok) o[(size_t)(first + c0 + pend_tt) * HV + h * s.V + col] = pend;
     __syncthreads();                              // this buffer is fetched into again next turn
   }
 #pragma unroll
