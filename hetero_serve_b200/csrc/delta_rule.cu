@@ -125,7 +125,8 @@ __global__ void delta_conv_state_kernel(float* __restrict__ state, const float* 
 }
 
 constexpr int DR_DP = 16;         // state rows a thread keeps
-constexpr int DR_THREADS = 256;
+constexpr int DR_STAGES = 3;      // chunks of tokens in shared memory
+constexpr int DR_THREADS = 64;   // few warps a block: the shared-memory pipe of an SM bounds a block's step from token to token
 
 __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
   const unsigned sa = (unsigned)__cvta_generic_to_shared(dst);
@@ -141,8 +142,8 @@ __device__ __forceinline__ void cp_async16(float* dst, const float* src) {
 // pieces of a row in shared memory (no bank conflict); they sum their shares with a butterfly.
 // The tokens' q, k, decay
 // rows (padded with zeros to KS*DP), v columns and betas come through shared memory a chunk of
-// CH tokens at a time, fetched asynchronously while the chunk before is worked on: the latency
-// of fetching them is off the token-to-token chain.
+// CH tokens at a time, fetched asynchronously two chunks ahead: the latency of fetching them is
+// off the token-to-token chain.
 __global__ void __launch_bounds__(DR_THREADS)
 delta_recurrence_kernel(float* __restrict__ o, float* __restrict__ state,
                         const float* __restrict__ qn, const float* __restrict__ kn,
@@ -174,7 +175,7 @@ delta_recurrence_kernel(float* __restrict__ o, float* __restrict__ state,
   }
   const int QK = s.kv_heads * s.D, HV = s.heads * s.V, HD = s.heads * s.D;
   const int first = req_start[r];
-  for (int i = threadIdx.x; i < 2 * per_buf; i += DR_THREADS) sm[i] = 0.f;   // the padding stays 0
+  for (int i = threadIdx.x; i < DR_STAGES * per_buf; i += DR_THREADS) sm[i] = 0.f;   // padding stays 0
   __syncthreads();
   auto fetch = [&](int buf, int c0) {
     float* b_k = sm + buf * per_buf;
@@ -210,16 +211,17 @@ delta_recurrence_kernel(float* __restrict__ o, float* __restrict__ state,
       cp_async4(b_b + threadIdx.x, beta + (size_t)(first + c0 + threadIdx.x) * s.heads + h);
     asm volatile("cp.async.commit_group;");
   };
+  // three buffers: while a chunk is worked on, the two behind it are on their way (a fetch
+  // takes longer than a chunk of tokens does).  Every turn commits a group, an empty one at
+  // the end, so that "all but the newest two have landed" always names the chunk of this turn.
   fetch(0, 0);
+  if (CH < n) fetch(1, CH); else asm volatile("cp.async.commit_group;");
   int buf = 0;
-  for (int c0 = 0; c0 < n; c0 += CH, buf ^= 1) {
+  for (int c0 = 0; c0 < n; c0 += CH, buf = (buf + 1) % DR_STAGES) {
     const int nc = min(CH, n - c0);
-    if (c0 + CH < n) {
-      fetch(buf ^ 1, c0 + CH);
-      asm volatile("cp.async.wait_group 1;");
-    } else {
-      asm volatile("cp.async.wait_group 0;");
-    }
+    if (c0 + 2 * CH < n) fetch((buf + 2) % DR_STAGES, c0 + 2 * CH);
+    else asm volatile("cp.async.commit_group;");
+    asm volatile("cp.async.wait_group 2;");
     __syncthreads();
     const float* b_k = sm + buf * per_buf;
     const float* b_q = b_k + CH * Dp;
@@ -397,7 +399,7 @@ HS_EXPORT int hs_delta_recurrence(float* o, float* state, const float* qn, const
   const int Dp = KS * hs::DR_DP;
   int CH = 1024 / Dp;                               // tokens a chunk: 3 * CH * Dp <= 3072 floats
   CH = CH < 2 ? 2 : (CH > 16 ? 16 : CH);
-  const size_t smem = 2 * (size_t)((3 * CH * Dp + CH * cols + CH + 3) & ~3) * sizeof(float);
+  const size_t smem = hs::DR_STAGES * (size_t)((3 * CH * Dp + CH * cols + CH + 3) & ~3) * sizeof(float);
   // 16-byte copies need rows of q, k and the decay that start on 16-byte boundaries
   const int vec = D % 4 == 0 && !((uintptr_t)qn & 15) && !((uintptr_t)kn & 15) &&
                   !((uintptr_t)decay & 15);
