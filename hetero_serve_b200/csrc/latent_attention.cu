@@ -7,8 +7,7 @@
 //   out_lat[h]  = sum_j weight_j * c_j                        (R numbers; W_uv[h] follows)
 //
 // The sink of a head is a learned logit without key or value: it only enters the denominator.
-// Scores, the running maximum, the denominator and the accumulator are float32.  A warp works on four
-// heads of a token at once (the key rows are the same for all heads).  A step of few
+// Scores, the running maximum, the denominator and the accumulator are float32.  A step of few
 // tokens splits each token's keys over several blocks whose shares (maximum, sum, weighted rows)
 // a second kernel merges; the split depends on the number of tokens in the step only.
 //
@@ -64,21 +63,17 @@ __global__ void latent_append_kernel(TC* __restrict__ pool, const float* __restr
 
 // -- attention ---------------------------------------------------------------------------------
 constexpr int LA_TILE = 32;     // keys per tile: one per lane when scores are formed
-constexpr int LA_HB = 8;        // heads per block
-constexpr int LA_HP = 4;        // heads per warp: a key value read from shared memory serves all
-constexpr int LA_NW = LA_HB / LA_HP;   // warps per block
+constexpr int LA_HB = 8;        // heads (warps) per block
 
 // Shared rows are padded to a multiple of 4 floats (zeros), read 16 bytes at a time.  Key rows
 // have a stride of 4 (mod 32) floats, so that the lanes of a quarter warp, each on a row of its
 // own while scores are formed, hit distinct banks; while the weighted rows are summed, lane l
-// owns the dims 4 l + 128 i .. + 3 and the lanes read neighbouring pieces of one row.  The pipe
-// that serves shared memory retires one 128-byte wavefront a cycle and an SM four FMA
-// instructions, so every piece of a key row that a warp reads is used for LA_HP heads.
+// owns the dims 4 l + 128 i .. + 3 and the lanes read neighbouring pieces of one row.
 __host__ __device__ inline int la_w4(int W) { return (W + 3) & ~3; }
 __host__ __device__ inline int la_stride(int W) { return ((la_w4(W) + 27) / 32) * 32 + 4; }
 
-template <typename TC, int RC>      // RC: accumulator floats a lane keeps per head, a multiple of 4
-__global__ void __launch_bounds__(LA_NW * 32)
+template <typename TC, int RC>      // RC: accumulator floats a lane keeps, a multiple of 4
+__global__ void __launch_bounds__(LA_HB * 32)
 latent_attention_kernel(float* __restrict__ out, const float* __restrict__ qa,
                         const float* __restrict__ qr, const TC* __restrict__ pool,
                         const int* __restrict__ table, const int* __restrict__ tok_pos,
@@ -97,8 +92,8 @@ latent_attention_kernel(float* __restrict__ out, const float* __restrict__ qa,
   if (r < 0) return;
   const int pos = tok_pos[t];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int h0 = blockIdx.y * LA_HB + warp * LA_HP;      // this warp's first head
-  const bool live = h0 < n_heads;
+  const int h = blockIdx.y * LA_HB + warp;
+  const bool live = h < n_heads;
   // queries of this block's heads
   for (int i = threadIdx.x; i < LA_HB * W4; i += blockDim.x) {
     const int hh = i / W4, d = i - hh * W4;
@@ -115,25 +110,21 @@ latent_attention_kernel(float* __restrict__ out, const float* __restrict__ qa,
     }
     s_q[i] = v;
   }
-  // alone, a block opens each head's running softmax with the sink (weight 1); as one of
-  // `nsplit` blocks over the keys it starts empty and the sink joins when the shares are merged
-  float m[LA_HP], l[LA_HP], acc[LA_HP][RC];
+  // alone, a block opens its running softmax with the sink (weight 1); as one of `nsplit`
+  // blocks over the keys it starts empty and the sink joins when the shares are merged
+  float m = nsplit > 1 ? -INFINITY : (live ? sink[h] : 0.f);
+  float l = nsplit > 1 ? 0.f : 1.f;
+  float acc[RC];
 #pragma unroll
-  for (int i = 0; i < LA_HP; ++i) {
-    m[i] = nsplit > 1 ? -INFINITY : (h0 + i < n_heads ? sink[h0 + i] : 0.f);
-    l[i] = nsplit > 1 ? 0.f : 1.f;
-#pragma unroll
-    for (int c = 0; c < RC; ++c) acc[i][c] = 0.f;
-  }
-  const float4* q4 = (const float4*)(s_q + warp * LA_HP * W4);
-  const int qs = W4 / 4;                         // float4s between two heads' queries
+  for (int i = 0; i < RC; ++i) acc[i] = 0.f;
+  const float4* q4 = (const float4*)(s_q + warp * W4);
   const int n_tiles = pos / LA_TILE + 1;
   const int per = (n_tiles + nsplit - 1) / nsplit;
   const int tile_lo = blockIdx.z * per, tile_hi = min(n_tiles, tile_lo + per);
   for (int base = tile_lo * LA_TILE; base < tile_hi * LA_TILE; base += LA_TILE) {
     __syncthreads();                            // the tile before has been used (and s_q is set)
     const int nk = min(LA_TILE, pos + 1 - base);
-    for (int j = warp; j < nk; j += LA_NW) {
+    for (int j = warp; j < nk; j += LA_HB) {
       const int kp = base + j;
       const int pi = kp / page_size;
       const int page = pi < max_pages ? table[(size_t)r * max_pages + pi] : -1;
@@ -148,78 +139,54 @@ latent_attention_kernel(float* __restrict__ out, const float* __restrict__ qa,
     }
     __syncthreads();
     if (!live) continue;
-    float sc[LA_HP];
+    float s = -INFINITY;
     if (lane < nk) {
       const float4* k4 = (const float4*)(s_k + lane * ks);
-      float d0[LA_HP], d1[LA_HP];
-#pragma unroll
-      for (int i = 0; i < LA_HP; ++i) d0[i] = d1[i] = 0.f;
-      for (int d = 0; d < qs; ++d) {
-        const float4 b = k4[d];
-#pragma unroll
-        for (int i = 0; i < LA_HP; ++i) {
-          const float4 a = q4[i * qs + d];
-          d0[i] = fmaf(a.x, b.x, d0[i]); d1[i] = fmaf(a.y, b.y, d1[i]);
-          d0[i] = fmaf(a.z, b.z, d0[i]); d1[i] = fmaf(a.w, b.w, d1[i]);
-        }
+      float d0 = 0.f, d1 = 0.f;
+      for (int d = 0; d < W4 / 4; ++d) {
+        const float4 a = q4[d], b = k4[d];
+        d0 = fmaf(a.x, b.x, d0); d1 = fmaf(a.y, b.y, d1);
+        d0 = fmaf(a.z, b.z, d0); d1 = fmaf(a.w, b.w, d1);
       }
-#pragma unroll
-      for (int i = 0; i < LA_HP; ++i) sc[i] = (d0[i] + d1[i]) * scale;
-    } else {
-#pragma unroll
-      for (int i = 0; i < LA_HP; ++i) sc[i] = -INFINITY;
+      s = (d0 + d1) * scale;
     }
-    float pj[LA_HP];
+    const float m_new = fmaxf(m, warp_max(s));
+    const float corr = expf(m - m_new);
+    const float pj = lane < nk ? expf(s - m_new) : 0.f;
+    l = l * corr + warp_sum(pj);
+    m = m_new;
 #pragma unroll
-    for (int i = 0; i < LA_HP; ++i) {
-      const float m_new = fmaxf(m[i], warp_max(sc[i]));
-      const float corr = expf(m[i] - m_new);
-      pj[i] = lane < nk ? expf(sc[i] - m_new) : 0.f;
-      l[i] = l[i] * corr + warp_sum(pj[i]);
-      m[i] = m_new;
-#pragma unroll
-      for (int c = 0; c < RC; ++c) acc[i][c] *= corr;
-    }
+    for (int i = 0; i < RC; ++i) acc[i] *= corr;
     for (int j = 0; j < nk; ++j) {
-      float w[LA_HP];
-#pragma unroll
-      for (int i = 0; i < LA_HP; ++i) w[i] = __shfl_sync(0xffffffffu, pj[i], j);
+      const float w = __shfl_sync(0xffffffffu, pj, j);
       const float* kr = s_k + j * ks + 4 * lane;
 #pragma unroll
-      for (int c = 0; c < RC / 4; ++c) {
-        if (4 * lane + 128 * c < R) {           // the piece lies within the padded row
-          const float4 v = *(const float4*)(kr + 128 * c);
-#pragma unroll
-          for (int i = 0; i < LA_HP; ++i) {
-            acc[i][4 * c] = fmaf(w[i], v.x, acc[i][4 * c]);
-            acc[i][4 * c + 1] = fmaf(w[i], v.y, acc[i][4 * c + 1]);
-            acc[i][4 * c + 2] = fmaf(w[i], v.z, acc[i][4 * c + 2]);
-            acc[i][4 * c + 3] = fmaf(w[i], v.w, acc[i][4 * c + 3]);
-          }
+      for (int i = 0; i < RC / 4; ++i) {
+        if (4 * lane + 128 * i < R) {           // the piece lies within the padded row
+          const float4 c = *(const float4*)(kr + 128 * i);
+          acc[4 * i] = fmaf(w, c.x, acc[4 * i]);
+          acc[4 * i + 1] = fmaf(w, c.y, acc[4 * i + 1]);
+          acc[4 * i + 2] = fmaf(w, c.z, acc[4 * i + 2]);
+          acc[4 * i + 3] = fmaf(w, c.w, acc[4 * i + 3]);
         }
       }
     }
   }
   if (!live) return;
+  float* dst;
+  float inv = 1.f;
+  if (nsplit > 1) {                             // this block's share: maximum, sum, weighted rows
+    float* ps = partial + (((size_t)t * n_heads + h) * nsplit + blockIdx.z) * (R + 2);
+    if (lane == 0) { ps[0] = m; ps[1] = l; }
+    dst = ps + 2;
+  } else {
+    inv = 1.0f / l;
+    dst = out + ((size_t)t * n_heads + h) * R;
+  }
 #pragma unroll
-  for (int i = 0; i < LA_HP; ++i) {
-    const int h = h0 + i;
-    if (h >= n_heads) continue;
-    float* dst;
-    float inv = 1.f;
-    if (nsplit > 1) {                           // this block's share: maximum, sum, weighted rows
-      float* ps = partial + (((size_t)t * n_heads + h) * nsplit + blockIdx.z) * (R + 2);
-      if (lane == 0) { ps[0] = m[i]; ps[1] = l[i]; }
-      dst = ps + 2;
-    } else {
-      inv = 1.0f / l[i];
-      dst = out + ((size_t)t * n_heads + h) * R;
-    }
-#pragma unroll
-    for (int c = 0; c < RC; ++c) {
-      const int d = 4 * lane + 128 * (c >> 2) + (c & 3);
-      if (d < R) dst[d] = acc[i][c] * inv;
-    }
+  for (int i = 0; i < RC; ++i) {
+    const int d = 4 * lane + 128 * (i >> 2) + (i & 3);
+    if (d < R) dst[d] = acc[i] * inv;
   }
 }
 
@@ -292,7 +259,7 @@ static int launch_latent_attention(float* out, const float* qa, const float* qr,
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   dim3 grid(n_tokens, (n_heads + hs::LA_HB - 1) / hs::LA_HB, nsplit);
-  kern<<<grid, hs::LA_NW * 32, smem, st>>>(out, qa, qr, (const TC*)pool, table, tok_pos, tok_req,
+  kern<<<grid, hs::LA_HB * 32, smem, st>>>(out, qa, qr, (const TC*)pool, table, tok_pos, tok_req,
                                            sink, n_heads, R, P, qr_stride, qr_hstride, qr_off,
                                            scale, page_size, num_pages, max_pages, status, nsplit,
                                            partial, freq, rot_dims);
