@@ -11,6 +11,9 @@
 // tokens splits each token's keys over several blocks whose shares (maximum, sum, weighted rows)
 // a second kernel merges; the split depends on the number of tokens in the step only.
 //
+// `plan` (may be null): the step's attention work lists; with it `n_tokens` blocks are launched
+// and block i works on the i-th single-query token of the plan, if there is one.
+//
 // Pool rows: [pages, page_size, R + P] in the cache type; row of position p of request r is
 // table[r, p / page_size] * page_size + p % page_size.
 #include "common.cuh"
@@ -81,13 +84,16 @@ latent_attention_kernel(float* __restrict__ out, const float* __restrict__ qa,
                         int n_heads, int R, int P, int qr_stride, int qr_hstride, int qr_off,
                         float scale, int page_size, int num_pages, int max_pages, int* status,
                         int nsplit, float* __restrict__ partial,
-                        const float* __restrict__ freq, int rot_dims) {
+                        const float* __restrict__ freq, int rot_dims,
+                        const int* __restrict__ plan) {
   extern __shared__ __align__(16) float smem[];
   const int W = R + P;
   const int W4 = la_w4(W), ks = la_stride(W);
   float* s_q = smem;                            // [LA_HB][W4]
   float* s_k = smem + LA_HB * W4;               // [LA_TILE][ks]
-  const int t = blockIdx.x;
+  // with a plan, only its single-query tokens are this kernel's (the tiles go elsewhere)
+  if (plan && (int)blockIdx.x >= plan[0]) return;
+  const int t = plan ? plan[4 + 3 * blockIdx.x] : blockIdx.x;
   const int r = tok_req[t];
   if (r < 0) return;
   const int pos = tok_pos[t];
@@ -194,8 +200,10 @@ latent_attention_kernel(float* __restrict__ out, const float* __restrict__ qa,
 __global__ void latent_merge_kernel(float* __restrict__ out, const float* __restrict__ partial,
                                     const float* __restrict__ sink,
                                     const int* __restrict__ tok_req, int n_heads, int R,
-                                    int nsplit) {
-  const int t = blockIdx.x, h = blockIdx.y;
+                                    int nsplit, const int* __restrict__ plan) {
+  if (plan && (int)blockIdx.x >= plan[0]) return;
+  const int t = plan ? plan[4 + 3 * blockIdx.x] : blockIdx.x;
+  const int h = blockIdx.y;
   if (tok_req[t] < 0) return;
   const float* ps = partial + ((size_t)t * n_heads + h) * nsplit * (R + 2);
   float m = sink[h];
@@ -250,7 +258,7 @@ static int launch_latent_attention(float* out, const float* qa, const float* qr,
                                    int qr_stride, int qr_hstride, int qr_off, float scale,
                                    int page_size, int num_pages, int max_pages, int* status,
                                    int nsplit, float* partial, const float* freq, int rot_dims,
-                                   cudaStream_t st) {
+                                   const int* plan, cudaStream_t st) {
   const int W = R + P;
   const size_t smem = ((size_t)hs::LA_HB * hs::la_w4(W) + (size_t)hs::LA_TILE * hs::la_stride(W)) *
                       sizeof(float);
@@ -262,11 +270,11 @@ static int launch_latent_attention(float* out, const float* qa, const float* qr,
   kern<<<grid, hs::LA_HB * 32, smem, st>>>(out, qa, qr, (const TC*)pool, table, tok_pos, tok_req,
                                            sink, n_heads, R, P, qr_stride, qr_hstride, qr_off,
                                            scale, page_size, num_pages, max_pages, status, nsplit,
-                                           partial, freq, rot_dims);
+                                           partial, freq, rot_dims, plan);
   HS_LAUNCH_CHECK();
   if (nsplit > 1) {
     hs::latent_merge_kernel<<<dim3(n_tokens, n_heads), 128, 0, st>>>(out, partial, sink, tok_req,
-                                                                     n_heads, R, nsplit);
+                                                                     n_heads, R, nsplit, plan);
     HS_LAUNCH_CHECK();
   }
   return HS_OK;
@@ -278,7 +286,7 @@ HS_EXPORT int hs_latent_attention(float* out, const float* qa, const float* qr, 
                                   int qr_stride, int qr_hstride, int qr_off, float scale,
                                   int page_size, int num_pages, int max_pages, int cache_dtype,
                                   int* status, int nsplit, float* partial, const float* freq,
-                                  int rot_dims, void* stream) {
+                                  int rot_dims, const int* plan, void* stream) {
   if (nsplit < 1 || (nsplit > 1 && !partial)) return HS_ERR_ARGUMENT;
   if (rot_dims < 0 || rot_dims % 2 || rot_dims > P || (rot_dims && !freq)) return HS_ERR_ARGUMENT;
   if (!out || !qa || !qr || !pool || !table || !tok_pos || !tok_req || !sink || !status)
@@ -291,7 +299,7 @@ HS_EXPORT int hs_latent_attention(float* out, const float* qa, const float* qr, 
   return launch_latent_attention<TC, RC>(out, qa, qr, pool, table, tok_pos, tok_req, sink,    \
                                          n_tokens, n_heads, R, P, qr_stride, qr_hstride,      \
                                          qr_off, scale, page_size, num_pages, max_pages,      \
-                                         status, nsplit, partial, freq, rot_dims, st)
+                                         status, nsplit, partial, freq, rot_dims, plan, st)
 #define HS_LA_RC(TC)                   \
   do {                                 \
     if (rc <= 4) HS_LA(TC, 4);         \

@@ -189,7 +189,9 @@ def _declare(lib) -> None:
         "hs_grouped_linear": [P, P, P, I, I, I, I, I, I, I, I, I, P],
         "hs_latent_append": [P, P, P, P, P, P, I, I, I, I, I, F, I, I, I, I, P, P, I, P],
         "hs_latent_attention": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, I, I, P, I,
-                                P, P, I, P],
+                                P, P, I, P, P],
+        "hs_latent_prefill_mma": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, I, P, P,
+                                  I, P],
         "hs_delta_prepare": [P] * 15 + [I] * 9 + [P],
         "hs_delta_recurrence": [P] * 10 + [I] * 8 + [P],
         "hs_delta_finish": [P, P, P, P, P, P, I, F, I, I, I, I, I, I, I, I, P],
@@ -282,6 +284,7 @@ class CudaOps:
         self.pdl = True            # programmatic dependent launch (see the property below)
         self._skinny_need: dict = {}
         self._moe_need: dict = {}
+        self.latent_mma = True      # prompt portions of latent attention on the tensor cores
         self.latent_splits = None   # blocks a token's keys are split over in latent attention
         #                             (None: chosen from the number of tokens in the step)
         self.sorted_experts = True  # many (token, expert) pairs in bfloat16: sorted by expert and
@@ -1035,13 +1038,16 @@ class CudaOps:
 
     def latent_attention(self, out, qa, qr, pool, table, tok_pos, tok_req, sink, *, n_heads,
                          rank, rot_dim, qr_head_stride, qr_offset, scale, page_size, status,
-                         freq=None, rot_dims=0):
+                         freq=None, rot_dims=0, plan=None):
         """Causal softmax attention with a sink over cache rows ``[c (rank) | kr (rot_dim)]``
         shared by all heads: score = (qa[t,h] . c + qr[t,h] . kr) * scale, the denominator
         also holds exp(sink[h]); ``out[t, h] = sum_j weight_j c_j`` ([T, n_heads * rank],
         float32).  ``qa`` [T, n_heads * rank] float32; head h's rotated query part is
         ``qr[t, qr_offset + h * qr_head_stride : + rot_dim]``; with ``freq`` it arrives
-        unrotated and its first ``rot_dims`` entries are rotated as they are read."""
+        unrotated and its first ``rot_dims`` entries are rotated as they are read.  With the
+        step's ``plan`` and a bfloat16 cache, the plan's tiles (prompt portions) run on the
+        tensor cores with the queries rounded to bfloat16, its single-query tokens on the CUDA
+        cores; without a plan every token runs on the CUDA cores."""
         _want(out, "out", torch.float32, 2)
         _want(qa, "qa", torch.float32, 2)
         _want(qr, "qr", torch.float32, 2)
@@ -1056,6 +1062,24 @@ class CudaOps:
             raise KernelError("latent_attention: the rotated query parts exceed qr's row")
         if pool.numel() % (page_size * W) or sink.shape[0] != n_heads:
             raise KernelError("latent_attention: pool or sink does not fit")
+        rot = int(rot_dims) if freq is not None else 0
+        n_pages = pool.numel() // (page_size * W)
+        listed = None
+        if (plan is not None and plan.tile_cap > 0 and pool.dtype == torch.bfloat16
+                and self.tensor_cores and self.latent_mma):
+            code = self.lib.hs_latent_prefill_mma(
+                _ptr(out), _ptr(qa), _ptr(qr), _ptr(pool), _ptr(table), _ptr(sink),
+                _ptr(plan.data), 4 + plan_decode_ints(plan.n_rows), plan.tile_cap, n_heads, rank,
+                rot_dim, qr.shape[1], int(qr_head_stride), int(qr_offset), float(scale),
+                page_size, n_pages, table.shape[1], _ptr(status), _ptr(freq), rot,
+                self._stream())
+            if code != -1:
+                _check(code, f"latent_prefill_mma(rank={rank},rot_dim={rot_dim})")
+                self.launches += 1
+                if plan.decode_cap == 0:
+                    return
+                listed = plan.data          # the CUDA-core kernel takes the single-query tokens
+                n = plan.decode_cap
         # few tokens: the keys of each are split over several blocks so that the device fills
         blocks = n * -(-n_heads // 8)
         nsplit = 1 if blocks >= self.sm_count else min(16, -(-2 * self.sm_count // blocks))
@@ -1063,15 +1087,17 @@ class CudaOps:
             nsplit = int(self.latent_splits)
         partial = None
         if nsplit > 1:
-            partial = self._scratch_buffer("latent_partial", n * n_heads * nsplit * (rank + 2),
+            # shares are kept by flat token index, whichever tokens this launch works on
+            partial = self._scratch_buffer("latent_partial",
+                                           out.shape[0] * n_heads * nsplit * (rank + 2),
                                            torch.float32)
         self.launches += 2 if nsplit > 1 else 1
         _check(self.lib.hs_latent_attention(
             _ptr(out), _ptr(qa), _ptr(qr), _ptr(pool), _ptr(table), _ptr(tok_pos), _ptr(tok_req),
             _ptr(sink), n, n_heads, rank, rot_dim, qr.shape[1], int(qr_head_stride),
-            int(qr_offset), float(scale), page_size, pool.numel() // (page_size * W),
+            int(qr_offset), float(scale), page_size, n_pages,
             table.shape[1], _DT[pool.dtype], _ptr(status), nsplit, _ptr(partial), _ptr(freq),
-            int(rot_dims) if freq is not None else 0, self._stream()),
+            rot, _ptr(listed), self._stream()),
             f"latent_attention(rank={rank},rot_dim={rot_dim})")
 
     # -- the gated delta rule ---------------------------------------------------------------

@@ -94,7 +94,7 @@ class LatentAttention(Mixer):
         ops.latent_attention(lat, qa, proj, cache.pool, cache.table, ctx.tok_pos, ctx.tok_req,
                              self.sink, n_heads=H, rank=R, rot_dim=P, qr_head_stride=D + P,
                              qr_offset=D, scale=self.scale, page_size=cache.page_size,
-                             status=ctx.status, **rot)
+                             status=ctx.status, plan=ctx.plan, **rot)
         att = ctx.buffer("latent_heads", (T, H * V), ctx.dtype)
         ops.grouped_linear(att, lat, self.w_expand)
         ops.linear(x, att, self.w_out, None, residual=x)

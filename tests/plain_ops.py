@@ -191,7 +191,7 @@ class PlainOps:
 
     def latent_attention(self, out, qa, qr, pool, table, tok_pos, tok_req, sink, *, n_heads,
                          rank, rot_dim, qr_head_stride, qr_offset, scale, page_size, status,
-                         freq=None, rot_dims=0):
+                         freq=None, rot_dims=0, plan=None):
         rows = pool.view(-1, page_size, rank + rot_dim)
         scale32 = float(torch.tensor(scale, dtype=torch.float32))
         for t in range(out.shape[0]):

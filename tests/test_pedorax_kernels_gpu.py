@@ -255,6 +255,39 @@ def test_latent_rotations_fused_into_append_and_attention(ops, plain):
     assert int(status.item()) == 0
 
 
+@pytest.mark.parametrize("rank, rot, heads", [(32, 8, 3), (48, 16, 8), (272, 24, 5), (16, 4, 70)])
+def test_latent_attention_prompt_portions_on_the_tensor_cores(ops, plain, rank, rot, heads):
+    """A step's plan sends a portion of 150 tokens (two tiles, the second one short) to the
+    tensor-core kernel and two single tokens of another request to the CUDA-core kernel; the
+    queries are rounded to bfloat16 there, which bounds the agreement.  Ranks above 256 run
+    with eight warps a block; 70 heads put one token's heads into two blocks."""
+    lat = _fill(ops, plain, (200, 33), rank, rot, BF16, seed=50)
+    lat.pool = lat.pool_dev.cpu().clone()
+    host_batch = [("a", 0, 50, 150), ("b", 1, 31, 2)]
+    n = 152
+    pos = torch.cat([torch.arange(50, 200), torch.arange(31, 33)]).to(I32)
+    req = torch.cat([torch.zeros(150), torch.ones(2)]).to(I32)
+    plan = ops.make_plan(host_batch, n, 16)
+    assert plan.tile_cap == 2 and plan.decode_cap == 2
+    stride = rot + 5
+    qa = rnd(n, heads * rank, seed=51, std=0.3)
+    qr = rnd(n, 2 + heads * stride, seed=52, std=0.3)
+    sink = rnd(heads, seed=53)
+    want = torch.zeros(n, heads * rank, dtype=torch.float64)
+    plain.latent_attention(want, qa, qr, lat.pool, lat.table, pos, req, sink, n_heads=heads,
+                           rank=rank, rot_dim=rot, qr_head_stride=stride, qr_offset=2, scale=0.2,
+                           page_size=16, status=None)
+    got = torch.full((n, heads * rank), 7.0, dtype=F32, device=DEV)
+    status = torch.zeros(1, dtype=I32, device=DEV)
+    before = ops.launches
+    ops.latent_attention(got, dev(qa), dev(qr), lat.pool_dev, dev(lat.table), dev(pos), dev(req),
+                         dev(sink), n_heads=heads, rank=rank, rot_dim=rot, qr_head_stride=stride,
+                         qr_offset=2, scale=0.2, page_size=16, status=status, plan=plan)
+    assert ops.launches - before >= 2 and int(status.item()) == 0
+    close(got[150:], want[150:], 2e-5)                       # the single tokens: float32 queries
+    close(got[:150], want[:150], 2e-2)
+
+
 def test_latent_attention_sink_takes_weight_without_a_value(ops, plain):
     lat = _fill(ops, plain, (40,), 24, 8, F32, seed=40)
     queries = [(0, 0), (0, 39)]
