@@ -13,7 +13,7 @@
 //     warp per output row with 16-byte loads (a matrix-vector product per pair);
 //   * many pairs in bfloat16: the pairs are sorted by expert on the device (no host round
 //     trip), and tiles of 64 pairs x 64 outputs of one expert go through mma.sync m16n8k16 with
-//     float32 accumulators; the down projection's rows are added into the stream per token in
+//     float32 accumulators (two stages of cp.async copies, fragments by ldmatrix); the down projection's rows are added into the stream per token in
 //     the order the experts were chosen, so a token's result does not depend on its neighbours.
 #include "common.cuh"
 
@@ -355,38 +355,45 @@ __device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, const uint
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
-// Loads a [64 rows x 32] bfloat16 tile into registers: thread i takes 16-byte pieces i and
-// i + 128 (piece c: row c / 4, columns 8 (c % 4) ..).  Rows at or beyond `rows` are zero.
-// `row_ptr(r)` gives the start of row r.
+// Copies a [64 rows x 32] bfloat16 tile into shared memory asynchronously: thread i takes the
+// 16-byte pieces i and i + 128 (piece c: row c / 4, columns 8 (c % 4) ..).  Rows at or beyond
+// `rows` are filled with zeros (a copy of zero source bytes).  `row_ptr(r)` gives the start of
+// row r; `any` is some valid address for the rows that are not read.
 template <typename RowPtr>
-__device__ __forceinline__ void tile_fetch(uint4* regs, RowPtr row_ptr, int rows, int k0) {
+__device__ __forceinline__ void tile_copy(__nv_bfloat16* s, RowPtr row_ptr, int rows, int k0,
+                                          const __nv_bfloat16* any) {
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
     const int c = threadIdx.x + 128 * j;
     const int r = c >> 2, col = (c & 3) * 8;
-    regs[j] = r < rows ? *(const uint4*)(row_ptr(r) + k0 + col) : make_uint4(0, 0, 0, 0);
+    const bool ok = r < rows;
+    const __nv_bfloat16* src = ok ? row_ptr(r) + k0 + col : any;
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(s + r * TS + col);
+    const int bytes = ok ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes));
   }
 }
-__device__ __forceinline__ void tile_store(__nv_bfloat16* s, const uint4* regs) {
-#pragma unroll
-  for (int j = 0; j < 2; ++j) {
-    const int c = threadIdx.x + 128 * j;
-    *(uint4*)(s + (c >> 2) * TS + (c & 3) * 8) = regs[j];
-  }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t* r, const __nv_bfloat16* p) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(a));
 }
 
 // One block: 64 rows of one expert's segment x 64 outputs.  NB = 2: gate and up together with
 // the activation as epilogue (out: bfloat16 rows); NB = 1: the down projection (out: float32).
 // A rows: `a` indexed through row_token when GATHER (the normed rows of the tokens), else the
-// sorted rows themselves.  4 warps, each 32 x 32 of the tile.
+// sorted rows themselves.  4 warps, each 32 x 32 of the tile.  Two stages of tiles in shared
+// memory (the next one is copied while this one is used); fragments come through ldmatrix.
 template <int NB, bool GATHER>
 __global__ void __launch_bounds__(128)
 moe_tiles_kernel(void* __restrict__ out, const __nv_bfloat16* __restrict__ a,
                  const __nv_bfloat16* __restrict__ w0, const __nv_bfloat16* __restrict__ w1,
                  const int* __restrict__ work, const int* __restrict__ row_token, int E,
                  int max_tiles, int N, int K, float limit) {
-  __shared__ __align__(16) __nv_bfloat16 s_a[TM * TS];
-  __shared__ __align__(16) __nv_bfloat16 s_b[NB][TN * TS];
+  __shared__ __align__(16) __nv_bfloat16 s_a[2][TM * TS];
+  __shared__ __align__(16) __nv_bfloat16 s_b[NB][2][TN * TS];
   const int tile = blockIdx.x;
   if (tile >= work[0]) return;
   const int e = work[1 + 2 * E + tile];
@@ -415,42 +422,45 @@ moe_tiles_kernel(void* __restrict__ out, const __nv_bfloat16* __restrict__ a,
       for (int j = 0; j < 4; ++j)
 #pragma unroll
         for (int c = 0; c < 4; ++c) acc[x][i][j][c] = 0.f;
-  uint4 ra[2], rb[NB][2];
-  tile_fetch(ra, a_row, rows, 0);
-  tile_fetch(rb[0], b0_row, ncols, 0);
-  if (NB == 2) tile_fetch(rb[NB - 1], b1_row, ncols, 0);
-  for (int k0 = 0; k0 < K; k0 += TK) {
-    __syncthreads();                              // the tile before has been used
-    tile_store(s_a, ra);
-    tile_store(s_b[0], rb[0]);
-    if (NB == 2) tile_store(s_b[NB - 1], rb[NB - 1]);
-    __syncthreads();
-    if (k0 + TK < K) {                            // the next tile travels while this one is used
-      tile_fetch(ra, a_row, rows, k0 + TK);
-      tile_fetch(rb[0], b0_row, ncols, k0 + TK);
-      if (NB == 2) tile_fetch(rb[NB - 1], b1_row, ncols, k0 + TK);
+  auto copy = [&](int buf, int k0) {
+    tile_copy(s_a[buf], a_row, rows, k0, a);
+    tile_copy(s_b[0][buf], b0_row, ncols, k0, w0);
+    if (NB == 2) tile_copy(s_b[NB - 1][buf], b1_row, ncols, k0, w0);
+    asm volatile("cp.async.commit_group;");
+  };
+  copy(0, 0);
+  int buf = 0;
+  // lane's row and column offsets inside a 16 x 16 (A) or two 8 x 16 (B) block for ldmatrix
+  const int a_r = lane & 15, a_c = (lane >> 4) * 8;
+  const int b_r = (lane & 7) + (lane >> 4) * 8, b_c = ((lane >> 3) & 1) * 8;
+  for (int k0 = 0; k0 < K; k0 += TK, buf ^= 1) {
+    if (k0 + TK < K) {
+      copy(buf ^ 1, k0 + TK);
+      asm volatile("cp.async.wait_group 1;");
+    } else {
+      asm volatile("cp.async.wait_group 0;");
     }
+    __syncthreads();
 #pragma unroll
     for (int kk = 0; kk < TK; kk += 16) {
       uint32_t fa[2][4];
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const __nv_bfloat16* p = s_a + (wm + 16 * i + g) * TS + kk + 2 * tq;
-        fa[i][0] = *(const uint32_t*)p;
-        fa[i][1] = *(const uint32_t*)(p + 8 * TS);
-        fa[i][2] = *(const uint32_t*)(p + 8);
-        fa[i][3] = *(const uint32_t*)(p + 8 * TS + 8);
-      }
+      for (int i = 0; i < 2; ++i)
+        ldmatrix_x4(fa[i], s_a[buf] + (wm + 16 * i + a_r) * TS + kk + a_c);
 #pragma unroll
       for (int x = 0; x < NB; ++x)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const __nv_bfloat16* p = s_b[x] + (wn + 8 * j + g) * TS + kk + 2 * tq;
-          uint32_t fb[2] = {*(const uint32_t*)p, *(const uint32_t*)(p + 8)};
+        for (int j = 0; j < 4; j += 2) {
+          uint32_t fb[4];                         // b0, b1 of column block j, then of j + 1
+          ldmatrix_x4(fb, s_b[x][buf] + (wn + 8 * j + b_r) * TS + kk + b_c);
 #pragma unroll
-          for (int i = 0; i < 2; ++i) mma_bf16(acc[x][i][j], fa[i], fb);
+          for (int i = 0; i < 2; ++i) {
+            mma_bf16(acc[x][i][j], fa[i], fb);
+            mma_bf16(acc[x][i][j + 1], fa[i], fb + 2);
+          }
         }
     }
+    __syncthreads();                              // this stage is copied into again next turn
   }
 #pragma unroll
   for (int i = 0; i < 2; ++i)
