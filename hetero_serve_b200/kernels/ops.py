@@ -187,6 +187,7 @@ def _declare(lib) -> None:
         "hs_scale": [P, ctypes.c_longlong, F, P],
         "hs_rotary_pairs": [P, P, P, P, I, I, I, I, I, I, P],
         "hs_grouped_linear": [P, P, P, I, I, I, I, I, I, I, I, I, P],
+        "hs_grouped_linear_mma": [P, P, P, I, I, I, I, I, I, I, I, P],
         "hs_latent_append": [P, P, P, P, P, P, I, I, I, I, I, F, I, I, I, I, P, P, I, P],
         "hs_latent_attention": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, I, I, P, I,
                                 P, P, I, P, P],
@@ -986,10 +987,12 @@ class CudaOps:
                                         stride, n_vec, vec_stride, offset, dims, self._stream()),
                "rotary_pairs")
 
-    def grouped_linear(self, out, a, w, *, a_offset=0, a_group_stride=None):
+    def grouped_linear(self, out, a, w, *, a_offset=0, a_group_stride=None, w_nk=None):
         """Block-diagonal linear: ``out[t, g*n + j] = sum_k a[t, a_offset + g*a_group_stride + k]
         * w[g, k, j]``.  ``a`` float32 (a group's input may be a slice of a wider row), ``w``
-        [groups, k, n] (k-major), ``out`` [T, groups * n] float32 or of w's type."""
+        [groups, k, n] (k-major), ``out`` [T, groups * n] float32 or of w's type.  ``w_nk`` is
+        the same weight as [groups, n, k] in bfloat16: with it, 64 tokens or more and k a
+        multiple of 32, the product runs on the tensor cores (``a`` rounded to bfloat16)."""
         _want(a, "a", torch.float32, 2)
         _want(w, "w", _FLOATS, 3)
         _want(out, "out", _FLOATS, 2)
@@ -1003,6 +1006,14 @@ class CudaOps:
         if out.dtype != torch.float32 and out.dtype != w.dtype:
             raise KernelError("grouped_linear: out is float32 or of the weights' type")
         self.launches += 1
+        if (w_nk is not None and T >= 64 and w_nk.dtype == torch.bfloat16 and self.tensor_cores
+                and tuple(w_nk.shape) == (groups, n, k) and w_nk.is_contiguous()):
+            code = self.lib.hs_grouped_linear_mma(_ptr(out), _ptr(a), _ptr(w_nk), T, a.shape[1],
+                                                  int(a_offset), gs, groups, n, k,
+                                                  _DT[out.dtype], self._stream())
+            if code != -1:
+                _check(code, f"grouped_linear_mma(groups={groups},n={n},k={k})")
+                return
         _check(self.lib.hs_grouped_linear(_ptr(out), _ptr(a), _ptr(w), T, a.shape[1],
                                           int(a_offset), gs, groups, n, k, _DT[w.dtype],
                                           _DT[out.dtype], self._stream()),

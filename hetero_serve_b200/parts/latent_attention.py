@@ -64,6 +64,11 @@ class LatentAttention(Mixer):
         # k-major per head: [H, D, R] maps q_plain to the latent, [H, R, V] maps it to a value
         self.w_absorb = tensors[n["uk"]].view(self.H, self.D, self.R).contiguous()
         self.w_expand = tensors[n["uv"]].view(self.H, self.V, self.R).transpose(1, 2).contiguous()
+        # the same two, [H, out, in], for the tensor-core form that prompt portions take
+        self.w_absorb_nk = self.w_expand_nk = None
+        if wq.dtype == torch.bfloat16:
+            self.w_absorb_nk = self.w_absorb.transpose(1, 2).contiguous()
+            self.w_expand_nk = tensors[n["uv"]].view(self.H, self.V, self.R).contiguous()
         self.sink = tensors[n["sink"]]
         self.w_out = tensors[n["o"]]
         i = torch.arange(self.rot_dims // 2, dtype=torch.float64)
@@ -89,14 +94,15 @@ class LatentAttention(Mixer):
                               ctx.tok_req, c_offset=self.q_width, rank=R, rot_dim=P,
                               eps=self.eps, page_size=cache.page_size, status=ctx.status, **rot)
         qa = ctx.buffer("latent_qa", (T, H * R), torch.float32)
-        ops.grouped_linear(qa, proj, self.w_absorb, a_offset=0, a_group_stride=D + P)
+        ops.grouped_linear(qa, proj, self.w_absorb, a_offset=0, a_group_stride=D + P,
+                           w_nk=self.w_absorb_nk)
         lat = ctx.buffer("latent_mix", (T, H * R), torch.float32)
         ops.latent_attention(lat, qa, proj, cache.pool, cache.table, ctx.tok_pos, ctx.tok_req,
                              self.sink, n_heads=H, rank=R, rot_dim=P, qr_head_stride=D + P,
                              qr_offset=D, scale=self.scale, page_size=cache.page_size,
                              status=ctx.status, plan=ctx.plan, **rot)
         att = ctx.buffer("latent_heads", (T, H * V), ctx.dtype)
-        ops.grouped_linear(att, lat, self.w_expand)
+        ops.grouped_linear(att, lat, self.w_expand, w_nk=self.w_expand_nk)
         ops.linear(x, att, self.w_out, None, residual=x)
 
 

@@ -153,7 +153,7 @@ class PlainOps:
                 seg[1::2] = b * c + a * s
                 buf[t, lo:lo + dims] = seg.to(buf.dtype)
 
-    def grouped_linear(self, out, a, w, *, a_offset=0, a_group_stride=None):
+    def grouped_linear(self, out, a, w, *, a_offset=0, a_group_stride=None, w_nk=None):
         groups, k, n = w.shape
         gs = k if a_group_stride is None else a_group_stride
         T = out.shape[0]

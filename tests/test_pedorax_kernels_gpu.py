@@ -93,6 +93,25 @@ def test_grouped_linear_on_slices(ops, plain, wdt, odt, tol):
     close(got, want, tol)
 
 
+@pytest.mark.parametrize("odt, tol", [(F32, 3e-2), (BF16, 8e-2)])
+@pytest.mark.parametrize("T, groups, k, n", [(150, 3, 64, 40), (64, 2, 32, 200), (129, 1, 96, 64)])
+def test_grouped_linear_on_the_tensor_cores(ops, plain, odt, tol, T, groups, k, n):
+    """Many tokens in bfloat16 with the weights also given n-major: tiles on the tensor cores;
+    the input is rounded to bfloat16 there, which bounds the agreement."""
+    a = rnd(T, 20 + groups * (k + 12) + T % 2, seed=8)      # an odd row length: no 16-byte loads
+    w = rnd(groups, k, n, seed=9, std=0.3).to(BF16)
+    want = torch.zeros(T, groups * n, dtype=torch.float64)
+    plain.grouped_linear(want, a, w, a_offset=20, a_group_stride=k + 12)
+    got = torch.zeros(T, groups * n, dtype=odt, device=DEV)
+    w_nk = w.transpose(1, 2).contiguous()
+    ops.grouped_linear(got, dev(a), dev(w), a_offset=20, a_group_stride=k + 12, w_nk=dev(w_nk))
+    close(got, want, tol)
+    exact = torch.zeros(T, groups * n, dtype=F32, device=DEV)
+    ops.grouped_linear(exact, dev(a), dev(w), a_offset=20, a_group_stride=k + 12)
+    close(exact, want, 1e-4)
+    assert (got.float() - exact).abs().max() > 0          # the other kernel did run
+
+
 # -- attention over a shared latent ---------------------------------------------------------------
 class Latent:
     """A cache of two requests on scattered pages, filled through latent_append."""
