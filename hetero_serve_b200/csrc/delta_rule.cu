@@ -44,7 +44,8 @@ delta_prepare_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __re
                      const float* __restrict__ a2, const float* __restrict__ dt_bias,
                      const float* __restrict__ A_log, const float* __restrict__ state,
                      const int* __restrict__ tok_req, const int* __restrict__ req_start,
-                     const int* __restrict__ req_slot, DeltaShape s) {
+                     const int* __restrict__ req_slot, DeltaShape s,
+                     const float* __restrict__ z_a) {
   extern __shared__ float s_c[];                 // [2 * kv_heads * D] q and k after conv and silu
   const int t = blockIdx.x;
   const int r = tok_req[t];
@@ -56,8 +57,12 @@ delta_prepare_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __re
     const int HD = s.heads * s.D;
     for (int i = threadIdx.x; i < HD; i += blockDim.x) {
       float z = 0.f;
+      if (z_a) {                                   // W_a2 a was formed as a matrix product
+        z = z_a[(size_t)t * HD + i];
+      } else {
 #pragma unroll 8
-      for (int k = 0; k < s.ra; ++k) z = fmaf(a2[(size_t)k * HD + i], row[s.a_off + k], z);
+        for (int k = 0; k < s.ra; ++k) z = fmaf(a2[(size_t)k * HD + i], row[s.a_off + k], z);
+      }
       z += dt_bias[i];
       decay[(size_t)t * HD + i] = expf(-expf(A_log[i / s.D]) * softplusf_(z));
     }
@@ -304,7 +309,7 @@ __global__ void __launch_bounds__(128)
 delta_finish_kernel(TO* __restrict__ out, const float* __restrict__ o,
                     const float* __restrict__ proj, const float* __restrict__ g2,
                     const float* __restrict__ norm_w, const int* __restrict__ tok_req,
-                    float eps, DeltaShape s) {
+                    float eps, DeltaShape s, const float* __restrict__ z_g) {
   __shared__ float red[4];
   extern __shared__ float s_gin[];                  // [rg]
   const int t = blockIdx.x, h = blockIdx.y;
@@ -324,8 +329,12 @@ delta_finish_kernel(TO* __restrict__ out, const float* __restrict__ o,
   for (int e = threadIdx.x; e < s.V; e += blockDim.x) {
     const float* gcol = g2 + (size_t)h * s.V + e;
     float z = 0.f;
+    if (z_g) {                                     // W_g2 g was formed as a matrix product
+      z = z_g[(size_t)t * HV + h * s.V + e];
+    } else {
 #pragma unroll 8
-    for (int k = 0; k < s.rg; ++k) z = fmaf(gcol[(size_t)k * HV], s_gin[k], z);
+      for (int k = 0; k < s.rg; ++k) z = fmaf(gcol[(size_t)k * HV], s_gin[k], z);
+    }
     out[(size_t)t * HV + h * s.V + e] = from_f<TO>(src[e] * inv * norm_w[e] * sigmoidf_(z));
   }
 }
@@ -354,7 +363,7 @@ HS_EXPORT int hs_delta_prepare(float* qn, float* kn, float* vv, float* beta, flo
                                const int* tok_req, const int* req_start, const int* req_len,
                                const int* req_slot, int n_tokens, int n_requests, int heads,
                                int kv_heads, int D, int V, int taps, int ra, int rg,
-                               void* stream) {
+                               const float* z_a, void* stream) {
   if (!qn || !kn || !vv || !beta || !decay || !proj || !conv_w || !a2 || !dt_bias || !A_log ||
       !state || !tok_req || !req_start || !req_len || !req_slot)
     return HS_ERR_ARGUMENT;
@@ -371,7 +380,7 @@ HS_EXPORT int hs_delta_prepare(float* qn, float* kn, float* vv, float* beta, flo
                          (int)smem);
   hs::delta_prepare_kernel<<<dim3(n_tokens, 3), 256, smem, st>>>(qn, kn, vv, beta, decay, proj, conv_w, a2,
                                                         dt_bias, A_log, state, tok_req, req_start,
-                                                        req_slot, s);
+                                                        req_slot, s, z_a);
   HS_LAUNCH_CHECK();
   if (taps > 1) {
     dim3 grid((C + 127) / 128, n_requests);
@@ -413,7 +422,7 @@ HS_EXPORT int hs_delta_recurrence(float* o, float* state, const float* qn, const
 HS_EXPORT int hs_delta_finish(void* out, const float* o, const float* proj, const float* g2,
                               const float* norm_w, const int* tok_req, int n_tokens, float eps,
                               int heads, int kv_heads, int D, int V, int taps, int ra, int rg,
-                              int out_dtype, void* stream) {
+                              int out_dtype, const float* z_g, void* stream) {
   if (!out || !o || !proj || !g2 || !norm_w || !tok_req) return HS_ERR_ARGUMENT;
   hs::DeltaShape s;
   int rc = delta_shape(&s, heads, kv_heads, D, V, taps, ra, rg);
@@ -422,10 +431,10 @@ HS_EXPORT int hs_delta_finish(void* out, const float* o, const float* proj, cons
   cudaStream_t st = (cudaStream_t)stream;
   if (out_dtype == HS_DT_F32)
     hs::delta_finish_kernel<float><<<dim3(n_tokens, heads), 128, rg * sizeof(float), st>>>(
-        (float*)out, o, proj, g2, norm_w, tok_req, eps, s);
+        (float*)out, o, proj, g2, norm_w, tok_req, eps, s, z_g);
   else if (out_dtype == HS_DT_BF16)
     hs::delta_finish_kernel<__nv_bfloat16><<<dim3(n_tokens, heads), 128, rg * sizeof(float), st>>>(
-        (__nv_bfloat16*)out, o, proj, g2, norm_w, tok_req, eps, s);
+        (__nv_bfloat16*)out, o, proj, g2, norm_w, tok_req, eps, s, z_g);
   else
     return HS_ERR_UNSUPPORTED;
   HS_LAUNCH_CHECK();

@@ -193,9 +193,9 @@ def _declare(lib) -> None:
                                 P, P, I, P, P],
         "hs_latent_prefill_mma": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, I, P, P,
                                   I, P],
-        "hs_delta_prepare": [P] * 15 + [I] * 9 + [P],
+        "hs_delta_prepare": [P] * 15 + [I] * 9 + [P, P],
         "hs_delta_recurrence": [P] * 10 + [I] * 8 + [P],
-        "hs_delta_finish": [P, P, P, P, P, P, I, F, I, I, I, I, I, I, I, I, P],
+        "hs_delta_finish": [P, P, P, P, P, P, I, F, I, I, I, I, I, I, I, I, P, P],
         "hs_moe_route": [P, P, P, P, P, I, I, I, I, I, I, I, P],
         "hs_moe_experts": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, F, I, P, P, P],
         "hs_moe_sorted_scratch": [I, I, I, I, I, I, P, P],
@@ -1118,11 +1118,12 @@ class CudaOps:
                 shape["a_rank"], shape["g_rank"])
 
     def delta_prepare(self, qn, kn, vv, beta, decay, proj, conv_w, a2, dt_bias, a_log, state,
-                      tok_req, req_start, req_len, req_slot, shape):
+                      tok_req, req_start, req_len, req_slot, shape, z_a=None):
         """From the fused projection rows ``[q | k | v | b | a | g]`` (float32): short causal
         convolution and silu on q, k, v (history before a portion from ``state``), unit q and k
         per head (q also times dim^-1/2), beta = sigmoid(b), decay = exp(-exp(a_log) *
-        softplus(a2 a + dt_bias)); then the convolution history in ``state`` moves on."""
+        softplus(a2 a + dt_bias)); then the convolution history in ``state`` moves on.
+        ``z_a`` [T, heads * dim] float32, if given, is ``a2 a`` formed beforehand."""
         for t, nm in ((qn, "qn"), (kn, "kn"), (vv, "vv"), (beta, "beta"), (decay, "decay"),
                       (proj, "proj")):
             _want(t, nm, torch.float32, 2)
@@ -1140,7 +1141,7 @@ class CudaOps:
             _ptr(qn), _ptr(kn), _ptr(vv), _ptr(beta), _ptr(decay), _ptr(proj), _ptr(conv_w),
             _ptr(a2), _ptr(dt_bias), _ptr(a_log), _ptr(state), _ptr(tok_req), _ptr(req_start),
             _ptr(req_len), _ptr(req_slot), proj.shape[0], req_start.shape[0], H, HK, D, V, taps,
-            ra, rg, self._stream()), "delta_prepare")
+            ra, rg, _ptr(z_a), self._stream()), "delta_prepare")
 
     def delta_recurrence(self, o, state, qn, kn, vv, beta, decay, req_start, req_len, req_slot,
                          shape):
@@ -1157,7 +1158,7 @@ class CudaOps:
             _ptr(req_start), _ptr(req_len), _ptr(req_slot), req_start.shape[0], H, HK, D, V,
             taps, ra, rg, self._stream()), f"delta_recurrence(dim={D},vdim={V})")
 
-    def delta_finish(self, out, o, proj, g2, norm_w, tok_req, eps, shape):
+    def delta_finish(self, out, o, proj, g2, norm_w, tok_req, eps, shape, z_g=None):
         """out = o / sqrt(mean(o^2) + eps) per head * norm_w * sigmoid(g2^T g); ``g2`` is
         [g_rank, heads * vdim] (and ``a2`` of :meth:`delta_prepare` [a_rank, heads * dim])."""
         H, HK, D, V, taps, ra, rg = self._delta_sizes(shape)
@@ -1169,7 +1170,7 @@ class CudaOps:
         self.launches += 1
         _check(self.lib.hs_delta_finish(
             _ptr(out), _ptr(o), _ptr(proj), _ptr(g2), _ptr(norm_w), _ptr(tok_req), out.shape[0],
-            float(eps), H, HK, D, V, taps, ra, rg, _DT[out.dtype], self._stream()),
+            float(eps), H, HK, D, V, taps, ra, rg, _DT[out.dtype], _ptr(z_g), self._stream()),
             "delta_finish")
 
     # -- routed feed-forward ---------------------------------------------------------------

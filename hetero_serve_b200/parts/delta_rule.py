@@ -66,6 +66,12 @@ class ChannelDeltaRule(Mixer):
         self.conv_w = torch.cat([t[p + "q.conv"], t[p + "k.conv"], t[p + "v.conv"]]).contiguous()
         # the kernels read these two with the summed index slowest
         self.a2, self.g2 = t[p + "a2"].t().contiguous(), t[p + "g2"].t().contiguous()
+        # prompt portions in bfloat16 form W_a2 a and W_g2 g as matrix products on the tensor
+        # cores (the checkpoint's bfloat16 values, as stored: [out, in])
+        self.a2_nk = self.g2_nk = None
+        if t[p + "q"].dtype == torch.bfloat16 and ra % 32 == 0 and rg % 32 == 0:
+            self.a2_nk = t[p + "a2"].to(torch.bfloat16).unsqueeze(0).contiguous()
+            self.g2_nk = t[p + "g2"].to(torch.bfloat16).unsqueeze(0).contiguous()
         self.dt_bias, self.a_log, self.norm_w = t[p + "dt_bias"], t[p + "A_log"], t[p + "norm"]
         self.w_out = t[p + "o"]
         self.shape = dict(heads=self.H, kv_heads=self.HK, dim=self.D, vdim=self.V,
@@ -86,14 +92,25 @@ class ChannelDeltaRule(Mixer):
         beta = ctx.buffer("delta_beta", (T, self.H), f32)
         decay = ctx.buffer("delta_decay", (T, self.H * self.D), f32)
         state = ctx.state()
+        z_a = z_g = None
+        if self.a2_nk is not None and T >= 64:
+            ra, rg = self.shape["a_rank"], self.shape["g_rank"]
+            z_a = ctx.buffer("delta_za", (T, self.H * self.D), f32)
+            ops.grouped_linear(z_a, proj, self.a2.unsqueeze(0), a_offset=self.channels + self.H,
+                               a_group_stride=ra, w_nk=self.a2_nk)
+            z_g = ctx.buffer("delta_zg", (T, self.H * self.V), f32)
+            ops.grouped_linear(z_g, proj, self.g2.unsqueeze(0),
+                               a_offset=self.channels + self.H + ra, a_group_stride=rg,
+                               w_nk=self.g2_nk)
         ops.delta_prepare(qn, kn, vv, beta, decay, proj, self.conv_w, self.a2, self.dt_bias,
                           self.a_log, state, ctx.tok_req, ctx.req_start, ctx.req_len,
-                          ctx.req_slot, self.shape)
+                          ctx.req_slot, self.shape, z_a=z_a)
         o = ctx.buffer("delta_o", (T, self.H * self.V), f32)
         ops.delta_recurrence(o, state, qn, kn, vv, beta, decay, ctx.req_start, ctx.req_len,
                              ctx.req_slot, self.shape)
         gated = ctx.buffer("delta_gated", (T, self.H * self.V), ctx.dtype)
-        ops.delta_finish(gated, o, proj, self.g2, self.norm_w, ctx.tok_req, self.eps, self.shape)
+        ops.delta_finish(gated, o, proj, self.g2, self.norm_w, ctx.tok_req, self.eps, self.shape,
+                         z_g=z_g)
         ops.linear(x, gated, self.w_out, None, residual=x)
 
 

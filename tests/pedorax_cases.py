@@ -82,8 +82,20 @@ CASE_D = {
     ],
 }
 
+# sizes that are multiples of 32, as the tensor-core kernels of prompt portions want them: the
+# sorted experts, the tile attention, the per-head products and the low-rank second projections
+CASE_E = {
+    "architecture": "Pedorax", "vocab": 90, "width": 64, "embedding": {"scale": 1.0},
+    "logit_scale": 0.5, "norm": {"eps": 1e-5},
+    "layers": [
+        {"type": "channel_delta", "mixer": _delta(2, 1, 16, 16, 4, 32, 32), "mlp": _moe(32, 4, 3, 2, 2, 3.0)},
+        {"type": "latent_attention", "mixer": _latent(4, 32, 16, 16, 32, 1000.0, 16, 0.15), "mlp": _moe(32, 4, 3, 2, 2, 3.0)},
+        {"type": "latent_attention", "mixer": _latent(2, 32, 16, 32, 32, 1000.0, 16, 0.15, kv_from=1), "mlp": None},
+    ],
+}
+
 CASES = {"case_a": (CASE_A, 11), "case_b": (CASE_B, 12), "case_c": (CASE_C, 13),
-         "case_d": (CASE_D, 14)}
+         "case_d": (CASE_D, 14), "case_e": (CASE_E, 15)}
 
 
 class Case:

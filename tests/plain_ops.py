@@ -213,7 +213,7 @@ class PlainOps:
                 out[t, h * rank:(h + 1) * rank] = ((e / den) @ c).to(out.dtype)
 
     def delta_prepare(self, qn, kn, vv, beta, decay, proj, conv_w, a2, dt_bias, a_log, state,
-                      tok_req, req_start, req_len, req_slot, shape):
+                      tok_req, req_start, req_len, req_slot, shape, z_a=None):
         H, HK, D, V = shape["heads"], shape["kv_heads"], shape["dim"], shape["vdim"]
         taps, ra = shape["taps"], shape["a_rank"]
         C = 2 * HK * D + H * V
@@ -239,7 +239,8 @@ class PlainOps:
                 vv[t] = y[2 * HK * D:].to(vv.dtype)
                 row = proj[t].to(self.cd)
                 beta[t] = torch.sigmoid(row[C:C + H]).to(beta.dtype)
-                z = row[C + H:C + H + ra] @ a2.to(self.cd) + dt_bias.to(self.cd)     # a2 [ra, H*D]
+                z = (row[C + H:C + H + ra] @ a2.to(self.cd) if z_a is None else z_a[t].to(self.cd)) \
+                    + dt_bias.to(self.cd)                                        # a2 [ra, H*D]
                 sp = torch.where(z > 30, z, torch.log1p(torch.exp(torch.clamp(z, max=30))))
                 rate = torch.exp(a_log.to(self.cd)).repeat_interleave(D)
                 decay[t] = torch.exp(-rate * sp).to(decay.dtype)
@@ -266,14 +267,16 @@ class PlainOps:
                     o[t, h * V:(h + 1) * V] = (S[h].T @ q).to(o.dtype)
             st[:H * D * V] = S.reshape(-1).to(st.dtype)
 
-    def delta_finish(self, out, o, proj, g2, norm_w, tok_req, eps, shape):
+    def delta_finish(self, out, o, proj, g2, norm_w, tok_req, eps, shape, z_g=None):
         H, HK, D, V = shape["heads"], shape["kv_heads"], shape["dim"], shape["vdim"]
         ra, rg = shape["a_rank"], shape["g_rank"]
         g_off = 2 * HK * D + H * V + H + ra
         T = out.shape[0]
         v = o[:T].to(self.cd).view(T, H, V)
         v = v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps) * norm_w.to(self.cd)
-        gate = torch.sigmoid(proj[:T, g_off:g_off + rg].to(self.cd) @ g2.to(self.cd))   # [rg, H*V]
+        zg = proj[:T, g_off:g_off + rg].to(self.cd) @ g2.to(self.cd) if z_g is None \
+            else z_g[:T].to(self.cd)                                             # g2 [rg, H*V]
+        gate = torch.sigmoid(zg)
         out.copy_((v.view(T, H * V) * gate).to(out.dtype))
 
     def moe_route(self, sel_idx, sel_w, h, w_router, tok_req, *, top, n_groups, keep):

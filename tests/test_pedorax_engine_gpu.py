@@ -81,6 +81,27 @@ def test_models_with_layers_of_one_kind(pedorax_one_kind, tmp_path, dtype):
     assert n > 10 and err < TOL[dtype], (err, where)
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_prompt_portions_on_the_tensor_core_kernels(pedorax_cases, tmp_path, dtype):
+    """Sizes the tile kernels take and prompts long enough for them (100 and 150 tokens at
+    once, then portions of 70 beside single tokens): in bfloat16 the sorted experts, the tile
+    attention, the per-head products and the low-rank second projections run as mma tiles."""
+    from hetero_serve_b200.kernels import CudaOps
+    case = pedorax_cases["case_e"]
+    reqs = {"a": case.tokens(100, 301), "b": case.tokens(150, 302), "c": case.tokens(9, 303)}
+    steps, index = traces.whole(reqs)
+    more, index2 = traces.portions({"d": case.tokens(160, 304)}, sizes=(70, 2, 70, 1, 17))
+    ops = CudaOps(DEV)
+    out = _replay(case, dtype, steps, tmp_path, max_tokens=256, ops=ops)
+    err, where, n = _worst(case, dtype, out, index, reqs)
+    assert n > 200 and err < TOL[dtype], (err, where)
+    if dtype == "bfloat16":
+        assert ops._moe_need and any(v[0] for v in ops._moe_need.values())   # the sorted path ran
+    out2 = _replay(case, dtype, more, tmp_path, max_tokens=192, ops=ops)
+    err, where, n = _worst(case, dtype, out2, index2, {"d": case.tokens(160, 304)})
+    assert err < TOL[dtype], (err, where)
+
+
 def _runner(case, dtype="float32", pages=16, slots=4, **kw):
     model, _ = load_model(case.dir, dtype, DEV)
     return Runner(model, num_pages=pages, page_size=16, max_requests=slots, dtype=model.dtype,
