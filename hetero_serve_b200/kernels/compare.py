@@ -38,7 +38,7 @@ class TimedOps:
             a.record()
             out = target(*args, **kw)
             b.record()
-            self._events.append((name, a, b, _work(name, args, kw, self.batch)))
+            self._events.append((name, a, b, _flops_and_bytes(name, args, kw, self.batch)))
             return out
         return timed
 
@@ -73,7 +73,7 @@ def _contexts(batch):
     return seen, rows
 
 
-def _work(name, args, kw, batch):
+def _flops_and_bytes(name, args, kw, batch):
     """(FLOPs, bytes) an operation has to do, from its arguments."""
     try:
         if name == "linear":
