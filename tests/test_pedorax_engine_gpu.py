@@ -151,6 +151,27 @@ def test_long_decoding(pedorax_cases):
             assert pc.rms_error(res.logits[0].cpu(), want[i]) < TOL["float32"], i
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_captured_steps_equal_eager_steps(pedorax_cases, dtype):
+    """The same steps through CUDA graphs (sizes rounded up to a class, padding rows, the state
+    restored after the run that precedes a capture) and launched one by one: a prompt of 100
+    tokens on the tile kernels, a portion beside a single token, then single tokens, each shape
+    twice so that a replayed graph is compared too."""
+    case = pedorax_cases["case_e"]
+    a, b = case.tokens(140, 401), case.tokens(30, 402)
+    eager, graphs = _runner(case, dtype, pages=24), _runner(case, dtype, pages=24, cuda_graphs=True)
+    plan = [[("a", a[:100], [99])], [("a", a[100:120], [0, 19]), ("b", b[:1], [0])],
+            [("a", a[120:121], [0]), ("b", b[1:2], [0])], [("a", a[121:122], [0]), ("b", b[2:3], [0])],
+            [("a", a[122:140], [17]), ("b", b[3:4], [0])], [("a2", a[:100], [99])]]
+    for step in plan:
+        entries = [StepEntry(r, t, w) for r, t, w in step]
+        want = eager.step(entries).logits.clone()
+        got = graphs.step([StepEntry(r, t, w) for r, t, w in step]).logits.clone()
+        for i in range(want.shape[0]):
+            assert pc.rms_error(got[i].cpu(), want[i].cpu()) < (2e-2 if dtype == "bfloat16" else 1e-5), step[0][0]
+    assert pc.rms_error(want[0].cpu(), case.logits(a, dtype)[99]) < TOL[dtype] * 3
+
+
 def _greedy(case, prompt, n, dtype="float32"):
     w = case.plain if dtype == "float32" else case.plain_bf16
     toks, out, margins = list(prompt), [], []
