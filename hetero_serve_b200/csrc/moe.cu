@@ -1,6 +1,7 @@
 // Routed feed-forward (mixture of experts).
 //
-// route    per token: z = W_r h in float32, s = sigmoid(z).  Experts form `n_groups` equal groups
+// route    per token: z = W_r h in float32 (or handed in, formed as one product over the step),
+//          s = sigmoid(z).  Experts form `n_groups` equal groups
 //          of neighbours; a group's score is the sum of its two largest s; only experts of the
 //          `keep` best groups are eligible; the `top` eligible experts with the largest s are
 //          chosen (the lower index wins a tie) with weights s / (sum of the chosen s + 1e-20).
@@ -73,7 +74,7 @@ template <typename TH>
 __global__ void __launch_bounds__(ROUTE_THREADS)
 moe_route_kernel(int* __restrict__ sel_idx, float* __restrict__ sel_w, const TH* __restrict__ h,
                  const float* __restrict__ w_router, const int* __restrict__ tok_req, int width,
-                 int E, int top, int n_groups, int keep) {
+                 int E, int top, int n_groups, int keep, const float* __restrict__ z_in) {
   extern __shared__ float smem[];
   float* s_h = smem;                // [width]
   float* s_s = smem + width;        // [E] scores (-1 once taken)
@@ -81,12 +82,17 @@ moe_route_kernel(int* __restrict__ sel_idx, float* __restrict__ sel_w, const TH*
   const int t = blockIdx.x;
   if (tok_req[t] < 0) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int k = threadIdx.x; k < width; k += ROUTE_THREADS) s_h[k] = to_f(h[(size_t)t * width + k]);
-  __syncthreads();
-  for (int e = warp; e < E; e += ROUTE_THREADS / 32) {
-    const float* wr = w_router + (size_t)e * width;
-    const float z = row_dot(wr, s_h, width, lane);
-    if (lane == 0) s_s[e] = 1.0f / (1.0f + expf(-z));
+  if (z_in) {                        // the logits were formed as one matrix product over the step
+    for (int e = threadIdx.x; e < E; e += ROUTE_THREADS)
+      s_s[e] = 1.0f / (1.0f + expf(-z_in[(size_t)t * E + e]));
+  } else {
+    for (int k = threadIdx.x; k < width; k += ROUTE_THREADS) s_h[k] = to_f(h[(size_t)t * width + k]);
+    __syncthreads();
+    for (int e = warp; e < E; e += ROUTE_THREADS / 32) {
+      const float* wr = w_router + (size_t)e * width;
+      const float z = row_dot(wr, s_h, width, lane);
+      if (lane == 0) s_s[e] = 1.0f / (1.0f + expf(-z));
+    }
   }
   __syncthreads();
   if (warp != 0) return;
@@ -470,7 +476,7 @@ __global__ void moe_combine_kernel(float* __restrict__ x, const float* __restric
 
 HS_EXPORT int hs_moe_route(int* sel_idx, float* sel_w, const void* h, const float* w_router,
                            const int* tok_req, int n_tokens, int width, int E, int top,
-                           int n_groups, int keep, int h_dtype, void* stream) {
+                           int n_groups, int keep, int h_dtype, const float* z_in, void* stream) {
   if (!sel_idx || !sel_w || !h || !w_router || !tok_req) return HS_ERR_ARGUMENT;
   if (E <= 0 || top <= 0 || top > 32 || n_groups <= 0 || E % n_groups || keep <= 0 ||
       keep > n_groups || top > keep * (E / n_groups))
@@ -481,11 +487,11 @@ HS_EXPORT int hs_moe_route(int* sel_idx, float* sel_w, const void* h, const floa
   cudaStream_t st = (cudaStream_t)stream;
   if (h_dtype == HS_DT_F32)
     hs::moe_route_kernel<float><<<n_tokens, hs::ROUTE_THREADS, smem, st>>>(
-        sel_idx, sel_w, (const float*)h, w_router, tok_req, width, E, top, n_groups, keep);
+        sel_idx, sel_w, (const float*)h, w_router, tok_req, width, E, top, n_groups, keep, z_in);
   else if (h_dtype == HS_DT_BF16)
     hs::moe_route_kernel<__nv_bfloat16><<<n_tokens, hs::ROUTE_THREADS, smem, st>>>(
         sel_idx, sel_w, (const __nv_bfloat16*)h, w_router, tok_req, width, E, top, n_groups,
-        keep);
+        keep, z_in);
   else
     return HS_ERR_UNSUPPORTED;
   HS_LAUNCH_CHECK();

@@ -196,7 +196,7 @@ def _declare(lib) -> None:
         "hs_delta_prepare": [P] * 15 + [I] * 9 + [P, P],
         "hs_delta_recurrence": [P] * 10 + [I] * 8 + [P],
         "hs_delta_finish": [P, P, P, P, P, P, I, F, I, I, I, I, I, I, I, I, P, P],
-        "hs_moe_route": [P, P, P, P, P, I, I, I, I, I, I, I, P],
+        "hs_moe_route": [P, P, P, P, P, I, I, I, I, I, I, I, P, P],
         "hs_moe_experts": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, F, I, P, P, P],
         "hs_moe_sorted_scratch": [I, I, I, I, I, I, P, P],
         "hs_sample": [P, P, P, P, P, P, P, I, I, P, P, P, P],
@@ -1174,9 +1174,10 @@ class CudaOps:
             "delta_finish")
 
     # -- routed feed-forward ---------------------------------------------------------------
-    def moe_route(self, sel_idx, sel_w, h, w_router, tok_req, *, top, n_groups, keep):
+    def moe_route(self, sel_idx, sel_w, h, w_router, tok_req, *, top, n_groups, keep, z=None):
         """Per token: sigmoid scores of float32 router logits, group-limited choice of ``top``
-        experts, weights normalised over the chosen ones."""
+        experts, weights normalised over the chosen ones.  ``z`` [T, experts] float32, if given,
+        holds the logits (formed as one matrix product over the step)."""
         _want(sel_idx, "sel_idx", torch.int32, 2)
         _want(sel_w, "sel_w", torch.float32, 2)
         _want(h, "h", _FLOATS, 2)
@@ -1187,7 +1188,7 @@ class CudaOps:
         self.launches += 1
         _check(self.lib.hs_moe_route(_ptr(sel_idx), _ptr(sel_w), _ptr(h), _ptr(w_router),
                                      _ptr(tok_req), sel_idx.shape[0], width, E, top, n_groups,
-                                     keep, _DT[h.dtype], self._stream()),
+                                     keep, _DT[h.dtype], _ptr(z), self._stream()),
                f"moe_route(experts={E},top={top},groups={n_groups},keep={keep})")
 
     def moe_experts(self, x, y, h, w_gate, w_up, w_down, sel_idx, sel_w, tok_req, *, limit):

@@ -44,6 +44,13 @@ class RoutedExperts(FeedForward):
 
     def bind(self, tensors):
         self.w_router = tensors[self.router_name]
+        # prompt portions in bfloat16 form the logits as one product on the tensor cores (exact
+        # products, float32 sums) when the router's values are bfloat16 numbers to begin with
+        self.w_router_lp = None
+        first = tensors[self._expert(0, "gate")]
+        low = self.w_router.to(torch.bfloat16)
+        if first.dtype == torch.bfloat16 and torch.equal(low.to(torch.float32), self.w_router):
+            self.w_router_lp = low.contiguous()
 
         def stack(which):          # [E, out, in], as stored: the summed index runs fastest
             return torch.stack([tensors[self._expert(e, which)]
@@ -54,8 +61,12 @@ class RoutedExperts(FeedForward):
         ops, T = ctx.ops, h.shape[0]
         idx = ctx.buffer("route_idx", (T, self.top), torch.int32)
         wts = ctx.buffer("route_w", (T, self.top), torch.float32)
+        z = None
+        if self.w_router_lp is not None and T >= 64:
+            z = ctx.buffer("route_z", (T, self.E), torch.float32)
+            ops.linear(z, h, self.w_router_lp)
         ops.moe_route(idx, wts, h, self.w_router, ctx.tok_req, top=self.top,
-                      n_groups=self.groups, keep=self.keep)
+                      n_groups=self.groups, keep=self.keep, z=z)
         y = ctx.buffer("expert_act", (T * self.top, self.ff), torch.float32)
         ops.moe_experts(x, y, h, self.w_gate, self.w_up, self.w_down, idx, wts, ctx.tok_req,
                         limit=self.limit)

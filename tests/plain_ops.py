@@ -279,13 +279,14 @@ class PlainOps:
         gate = torch.sigmoid(zg)
         out.copy_((v.view(T, H * V) * gate).to(out.dtype))
 
-    def moe_route(self, sel_idx, sel_w, h, w_router, tok_req, *, top, n_groups, keep):
+    def moe_route(self, sel_idx, sel_w, h, w_router, tok_req, *, top, n_groups, keep, z=None):
         E = w_router.shape[0]
         per = E // n_groups
         for t in range(sel_idx.shape[0]):
             if int(tok_req[t]) < 0:
                 continue
-            s = torch.sigmoid(w_router.to(self.cd) @ h[t].to(self.cd))
+            s = torch.sigmoid(w_router.to(self.cd) @ h[t].to(self.cd) if z is None
+                              else z[t].to(self.cd))
             gs = torch.topk(s.view(n_groups, per), min(2, per), dim=-1).values.sum(-1)
             kept = torch.zeros(n_groups, dtype=torch.bool)
             kept[torch.topk(gs, keep).indices] = True

@@ -456,6 +456,15 @@ def test_route(ops, plain, E, top, groups, keep, hdt):
         assert a.keys() == b.keys(), t
         assert max(abs(a[k] - b[k]) for k in a) < 1e-5
         assert gw[t, 0] >= gw[t, -1]                            # largest score first
+    # the same choice when the logits are handed in (formed elsewhere as one matrix product)
+    z = (h.double() @ wr.double().T).float()
+    gi2 = torch.full((T, top), -7, dtype=I32, device=DEV)
+    gw2 = torch.zeros(T, top, dtype=F32, device=DEV)
+    ops.moe_route(gi2, gw2, dev(h), dev(wr), dev(req), top=top, n_groups=groups, keep=keep,
+                  z=dev(z))
+    keep_rows = [t for t in range(T) if t != 5]
+    assert torch.equal(gi2.cpu()[keep_rows].sort(-1).values, gi[keep_rows].sort(-1).values)
+    assert (gw2.cpu()[keep_rows].sort(-1).values - gw[keep_rows].sort(-1).values).abs().max() < 1e-5
 
 
 def test_route_bars_the_best_expert_of_a_weak_group(ops):
