@@ -1,3 +1,4 @@
 """Importing this package registers every architecture the framework ships."""
 from . import gpt2  # noqa: F401
 from . import pedorax  # noqa: F401
+from . import putelix  # noqa: F401

@@ -31,6 +31,9 @@
 #define HS_ACT_NONE 0
 #define HS_ACT_GELU_TANH 1
 #define HS_ACT_GELU_ERF 2
+#define HS_ACT_RELU2 3      // max(u, 0)^2
+#define HS_ACT_SILU 4       // u * sigmoid(u)
+#define HS_ACT_LAST HS_ACT_SILU
 
 #define HS_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -87,6 +90,8 @@ __device__ __forceinline__ float gelu_erf(float u) {
 __device__ __forceinline__ float apply_act(float u, int act) {
   if (act == HS_ACT_GELU_TANH) return gelu_tanh(u);
   if (act == HS_ACT_GELU_ERF) return gelu_erf(u);
+  if (act == HS_ACT_RELU2) { const float r = fmaxf(u, 0.f); return r * r; }
+  if (act == HS_ACT_SILU) return u / (1.0f + expf(-u));
   return u;
 }
 

@@ -337,7 +337,7 @@ HS_EXPORT int hs_linear_simt(void* out, const void* a, const void* w, const floa
   if (!out || !a || !w) return HS_ERR_ARGUMENT;
   if (M <= 0 || N <= 0) return HS_OK;
   if (K <= 0) return HS_ERR_ARGUMENT;
-  if (act < HS_ACT_NONE || act > HS_ACT_GELU_ERF) return HS_ERR_UNSUPPORTED;
+  if (act < HS_ACT_NONE || act > HS_ACT_LAST) return HS_ERR_UNSUPPORTED;
   dim3 grid((N + hs::LS_BN - 1) / hs::LS_BN, (M + hs::LS_BM - 1) / hs::LS_BM);
   if (grid.y > 65535) return HS_ERR_UNSUPPORTED;
   cudaStream_t st = (cudaStream_t)stream;

@@ -678,7 +678,7 @@ HS_EXPORT int hs_linear_skinny(void* out, const void* a, const float* x, const f
   if (((uintptr_t)w & 15) || (a && ((uintptr_t)a & 15)) || (x && ((uintptr_t)x & 15)) ||
       (gamma && ((uintptr_t)gamma & 15)) || (beta && ((uintptr_t)beta & 15)))
     return HS_ERR_UNSUPPORTED;
-  if (act < HS_ACT_NONE || act > HS_ACT_GELU_ERF) return HS_ERR_UNSUPPORTED;
+  if (act < HS_ACT_NONE || act > HS_ACT_LAST) return HS_ERR_UNSUPPORTED;
   if (out_dtype != HS_DT_F32 && out_dtype != HS_DT_BF16) return HS_ERR_UNSUPPORTED;
   if (pl.ksplit > 1 && (!scratch || !counters)) return HS_ERR_ARGUMENT;
   SkinnyParams p;

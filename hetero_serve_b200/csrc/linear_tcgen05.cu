@@ -78,6 +78,8 @@ __device__ __forceinline__ float act_tc(float u, int act) {
     return 0.5f * u * (1.0f + tanh_fast(inner));
   }
   if (act == HS_ACT_GELU_ERF) return gelu_erf(u);
+  if (act == HS_ACT_RELU2) { const float r = fmaxf(u, 0.f); return r * r; }
+  if (act == HS_ACT_SILU) return u / (1.0f + expf(-u));
   return u;
 }
 __device__ __forceinline__ void epi_bar_sync() {   // the 8 epilogue warps only
@@ -142,6 +144,12 @@ __device__ __forceinline__ void finish_row32(const TcParams& p, const uint32_t (
   } else if (p.act == HS_ACT_GELU_ERF) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) f[j] = act_tc(f[j], HS_ACT_GELU_ERF);
+  } else if (p.act == HS_ACT_RELU2) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = act_tc(f[j], HS_ACT_RELU2);
+  } else if (p.act == HS_ACT_SILU) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = act_tc(f[j], HS_ACT_SILU);
   }
   const size_t off = (size_t)row * p.N + nbase;
   if (p.residual) {
@@ -187,6 +195,12 @@ __device__ __forceinline__ void bias_act32(const TcParams& p, const uint32_t (&v
   } else if (p.act == HS_ACT_GELU_ERF) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) f[j] = act_tc(f[j], HS_ACT_GELU_ERF);
+  } else if (p.act == HS_ACT_RELU2) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = act_tc(f[j], HS_ACT_RELU2);
+  } else if (p.act == HS_ACT_SILU) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = act_tc(f[j], HS_ACT_SILU);
   }
 }
 
@@ -536,6 +550,12 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
               } else if (p.act == HS_ACT_GELU_ERF) {
 #pragma unroll
                 for (int j = 0; j < 4; ++j) x[j] = act_tc(x[j], HS_ACT_GELU_ERF);
+              } else if (p.act == HS_ACT_RELU2) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) x[j] = act_tc(x[j], HS_ACT_RELU2);
+              } else if (p.act == HS_ACT_SILU) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) x[j] = act_tc(x[j], HS_ACT_SILU);
               }
               if (p.residual) {
                 x[0] += r4.x; x[1] += r4.y; x[2] += r4.z; x[3] += r4.w;
@@ -982,6 +1002,12 @@ linear_tcgen05_cluster_kernel(const __grid_constant__ CUtensorMap map_a,
       } else if (p.act == HS_ACT_GELU_ERF) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) x[j] = act_tc(x[j], HS_ACT_GELU_ERF);
+      } else if (p.act == HS_ACT_RELU2) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) x[j] = act_tc(x[j], HS_ACT_RELU2);
+      } else if (p.act == HS_ACT_SILU) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) x[j] = act_tc(x[j], HS_ACT_SILU);
       }
       x[0] += r4.x; x[1] += r4.y; x[2] += r4.z; x[3] += r4.w;
       if (vec4) {
@@ -1286,7 +1312,7 @@ HS_EXPORT int hs_linear_tcgen05(void* out, const void* a, const void* w, const f
   if (((uintptr_t)a & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15)) return HS_ERR_UNSUPPORTED;
   if (residual && ((uintptr_t)residual & 15)) return HS_ERR_UNSUPPORTED;
   if (bias && ((uintptr_t)bias & 15)) return HS_ERR_UNSUPPORTED;
-  if (act < HS_ACT_NONE || act > HS_ACT_GELU_ERF) return HS_ERR_UNSUPPORTED;
+  if (act < HS_ACT_NONE || act > HS_ACT_LAST) return HS_ERR_UNSUPPORTED;
   if (out_dtype != HS_DT_F32 && out_dtype != HS_DT_BF16) return HS_ERR_UNSUPPORTED;
   TcPlan pl;
   if (!plan_tc(M, N, K, tile_n, pair, pl)) return HS_ERR_UNSUPPORTED;

@@ -8,6 +8,10 @@
 // expert   g = min(W_g h, limit), u = clamp(W_u h, -limit, limit), y = g * sigmoid(1.702 g) * (u + 1)
 // layer    x += sum_k weight_k * (W_d[e_k] y_k), experts in the order they were chosen
 //
+// A second routing rule (route_top): z = W_r h + b in float32, the `top` largest logits are chosen
+// (the lower index wins a tie) and weighted by the softmax over the chosen logits alone; and a
+// second expert activation (act 1): y = silu(W_g h) * (W_u h), no limit.
+//
 // Expert matrices are stacked as they are stored: gate / up [E, ff, width], down [E, width, ff]
 // (the summed index runs fastest).  Two paths:
 //   * few (token, expert) pairs, and all of float32: every pair streams its expert's rows, one
@@ -137,7 +141,60 @@ moe_route_kernel(int* __restrict__ sel_idx, float* __restrict__ sel_w, const TH*
   }
 }
 
-__device__ __forceinline__ float expert_act(float g, float u, float limit) {
+// One block per token: z = W_r h + b (or handed in), the `top` largest, softmax over the chosen.
+template <typename TH>
+__global__ void __launch_bounds__(ROUTE_THREADS)
+moe_route_top_kernel(int* __restrict__ sel_idx, float* __restrict__ sel_w,
+                     const TH* __restrict__ h, const float* __restrict__ w_router,
+                     const float* __restrict__ bias, const int* __restrict__ tok_req, int width,
+                     int E, int top, const float* __restrict__ z_in) {
+  extern __shared__ float smem[];
+  float* s_h = smem;                // [width]
+  float* s_z = smem + width;        // [E] logits (-inf once taken)
+  const int t = blockIdx.x;
+  if (tok_req[t] < 0) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (z_in) {
+    for (int e = threadIdx.x; e < E; e += ROUTE_THREADS)
+      s_z[e] = z_in[(size_t)t * E + e] + (bias ? bias[e] : 0.f);
+  } else {
+    for (int k = threadIdx.x; k < width; k += ROUTE_THREADS) s_h[k] = to_f(h[(size_t)t * width + k]);
+    __syncthreads();
+    for (int e = warp; e < E; e += ROUTE_THREADS / 32) {
+      const float z = row_dot(w_router + (size_t)e * width, s_h, width, lane);
+      if (lane == 0) s_z[e] = z + (bias ? bias[e] : 0.f);
+    }
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  float chosen_v = -INFINITY;                          // lane k keeps the k-th choice (top <= 32)
+  int chosen_i = 0;
+  for (int round = 0; round < top; ++round) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = s_z[e];
+      if (v > bv || (bi == 0x7fffffff && v == v)) { bv = v; bi = e; }
+    }
+    warp_argmax(bv, bi);
+    if (lane == round) { chosen_v = bv; chosen_i = bi; }
+    if (lane == 0 && bi < E) s_z[bi] = -INFINITY;      // taken
+    __syncwarp();
+  }
+  // softmax over the chosen logits: the first choice is the largest
+  const float top_v = __shfl_sync(0xffffffffu, chosen_v, 0);
+  const float ex = lane < top ? expf(chosen_v - top_v) : 0.f;
+  float total = 0.f;
+  for (int k = 0; k < top; ++k) total += __shfl_sync(0xffffffffu, ex, k);
+  if (lane < top) {
+    sel_idx[(size_t)t * top + lane] = chosen_i;
+    sel_w[(size_t)t * top + lane] = ex / total;
+  }
+}
+
+// act 0: the clamped form above; act 1: silu(g) * u
+__device__ __forceinline__ float expert_act(float g, float u, float limit, int act) {
+  if (act == 1) return g / (1.0f + expf(-g)) * u;
   g = fminf(g, limit);
   u = fminf(fmaxf(u, -limit), limit);
   return g * (1.0f / (1.0f + expf(-1.702f * g))) * (u + 1.0f);
@@ -200,7 +257,7 @@ __global__ void __launch_bounds__(GEMV_THREADS)
 moe_gate_up_rows_kernel(float* __restrict__ y, const TW* __restrict__ h,
                         const TW* __restrict__ w_gate, const TW* __restrict__ w_up,
                         const int* __restrict__ sel_idx, const int* __restrict__ tok_req,
-                        int width, int ff, int top, int E, float limit) {
+                        int width, int ff, int top, int E, float limit, int act) {
   extern __shared__ __align__(16) float s_h[];         // [width]
   const int pair = blockIdx.x;
   const int t = pair / top;
@@ -225,7 +282,7 @@ moe_gate_up_rows_kernel(float* __restrict__ y, const TW* __restrict__ h,
 #pragma unroll
   for (int i = 0; i < PER; ++i) {
     const int f = f0 + i * NW;
-    if (lane == 0 && f < ff) y[(size_t)pair * ff + f] = expert_act(res[2 * i], res[2 * i + 1], limit);
+    if (lane == 0 && f < ff) y[(size_t)pair * ff + f] = expert_act(res[2 * i], res[2 * i + 1], limit, act);
   }
 }
 
@@ -362,7 +419,7 @@ __global__ void __launch_bounds__(128)
 moe_tiles_kernel(void* __restrict__ out, const __nv_bfloat16* __restrict__ a,
                  const __nv_bfloat16* __restrict__ w0, const __nv_bfloat16* __restrict__ w1,
                  const int* __restrict__ work, const int* __restrict__ row_token, int E,
-                 int max_tiles, int N, int K, float limit) {
+                 int max_tiles, int N, int K, float limit, int act) {
   __shared__ __align__(16) __nv_bfloat16 s_a[2][TM * TS];
   __shared__ __align__(16) __nv_bfloat16 s_b[NB][2][TN * TS];
   const int tile = blockIdx.x;
@@ -448,7 +505,7 @@ moe_tiles_kernel(void* __restrict__ out, const __nv_bfloat16* __restrict__ a,
           const size_t at = (size_t)(row0 + r) * N + n0 + c + q;
           if (NB == 2)
             ((__nv_bfloat16*)out)[at] = __float2bfloat16_rn(
-                expert_act(acc[0][i][j][2 * half + q], acc[NB - 1][i][j][2 * half + q], limit));
+                expert_act(acc[0][i][j][2 * half + q], acc[NB - 1][i][j][2 * half + q], limit, act));
           else
             ((float*)out)[at] = acc[0][i][j][2 * half + q];
         }
@@ -498,6 +555,27 @@ HS_EXPORT int hs_moe_route(int* sel_idx, float* sel_w, const void* h, const floa
   return HS_OK;
 }
 
+HS_EXPORT int hs_moe_route_top(int* sel_idx, float* sel_w, const void* h, const float* w_router,
+                               const float* bias, const int* tok_req, int n_tokens, int width,
+                               int E, int top, int h_dtype, const float* z_in, void* stream) {
+  if (!sel_idx || !sel_w || !h || !w_router || !tok_req) return HS_ERR_ARGUMENT;
+  if (E <= 0 || top <= 0 || top > 32 || top > E) return HS_ERR_UNSUPPORTED;
+  if (n_tokens <= 0) return HS_OK;
+  const size_t smem = (size_t)(width + E) * sizeof(float);
+  if (smem > 48 * 1024) return HS_ERR_UNSUPPORTED;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (h_dtype == HS_DT_F32)
+    hs::moe_route_top_kernel<float><<<n_tokens, hs::ROUTE_THREADS, smem, st>>>(
+        sel_idx, sel_w, (const float*)h, w_router, bias, tok_req, width, E, top, z_in);
+  else if (h_dtype == HS_DT_BF16)
+    hs::moe_route_top_kernel<__nv_bfloat16><<<n_tokens, hs::ROUTE_THREADS, smem, st>>>(
+        sel_idx, sel_w, (const __nv_bfloat16*)h, w_router, bias, tok_req, width, E, top, z_in);
+  else
+    return HS_ERR_UNSUPPORTED;
+  HS_LAUNCH_CHECK();
+  return HS_OK;
+}
+
 // Scratch of the sorted path for n_tokens x top pairs: ints (work lists, pair positions, row
 // tokens) and bytes of rows (bfloat16 activations, then float32 outputs of the down projection).
 // Returns 0 and zeros when the sorted path does not take the shape.
@@ -519,11 +597,11 @@ HS_EXPORT int hs_moe_sorted_scratch(int n_tokens, int width, int ff, int top, in
 HS_EXPORT int hs_moe_experts(float* x, float* y, const void* h, const void* w_gate,
                              const void* w_up, const void* w_down, const int* sel_idx,
                              const float* sel_w, const int* tok_req, int n_tokens, int width,
-                             int ff, int top, int E, float limit, int dtype, int* ints,
+                             int ff, int top, int E, float limit, int act_kind, int dtype, int* ints,
                              void* rows, void* stream) {
   if (!x || !h || !w_gate || !w_up || !w_down || !sel_idx || !sel_w || !tok_req)
     return HS_ERR_ARGUMENT;
-  if (width <= 0 || ff <= 0 || top <= 0 || E <= 0) return HS_ERR_UNSUPPORTED;
+  if (width <= 0 || ff <= 0 || top <= 0 || E <= 0 || act_kind < 0 || act_kind > 1) return HS_ERR_UNSUPPORTED;
   if (n_tokens <= 0) return HS_OK;
   cudaStream_t st = (cudaStream_t)stream;
   if (ints && rows) {
@@ -543,11 +621,11 @@ HS_EXPORT int hs_moe_experts(float* x, float* y, const void* h, const void* w_ga
     const __nv_bfloat16* hb = (const __nv_bfloat16*)h;
     hs::moe_tiles_kernel<2, true><<<dim3(max_tiles, (ff + hs::TN - 1) / hs::TN), 128, 0, st>>>(
         act, hb, (const __nv_bfloat16*)w_gate, (const __nv_bfloat16*)w_up, work, row_token, E,
-        max_tiles, ff, width, limit);
+        max_tiles, ff, width, limit, act_kind);
     HS_LAUNCH_CHECK();
     hs::moe_tiles_kernel<1, false><<<dim3(max_tiles, (width + hs::TN - 1) / hs::TN), 128, 0, st>>>(
         down, act, (const __nv_bfloat16*)w_down, nullptr, work, row_token, E, max_tiles, width,
-        ff, limit);
+        ff, limit, act_kind);
     HS_LAUNCH_CHECK();
     hs::moe_combine_kernel<<<n_tokens, 256, 0, st>>>(x, down, pair_pos, sel_w, tok_req, width,
                                                      top);
@@ -570,7 +648,7 @@ HS_EXPORT int hs_moe_experts(float* x, float* y, const void* h, const void* w_ga
       cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_y);      \
     k1<<<g1, hs::GEMV_THREADS, smem_h, st>>>(y, (const TW*)h, (const TW*)w_gate,               \
                                              (const TW*)w_up, sel_idx, tok_req, width, ff,     \
-                                             top, E, limit);                                   \
+                                             top, E, limit, act_kind);                         \
     HS_LAUNCH_CHECK();                                                                         \
     k2<<<g2, hs::GEMV_THREADS, smem_y, st>>>(x, y, (const TW*)w_down, sel_idx, sel_w, tok_req, \
                                              width, ff, top, E);                               \

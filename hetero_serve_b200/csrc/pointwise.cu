@@ -6,6 +6,9 @@
 //            turns by the angle p * f_i:  (u c - v s, v c + u s),  f_i = base^(-2i/dims).
 //            The table f (dims/2 floats) comes from the host, formed in double.  The angle is
 //            formed in double and reduced there, so that its error does not grow with p.
+//   gated:   out[t, f] = act(gu[t, f]) * gu[t, ff + f] * s_t  with  s_t = sigmoid(h[t] . w_s)
+//            (one number per token; 1 without w_s): the middle of a gated feed-forward whose
+//            gate and up projections came as one product [gate | up].
 #include "common.cuh"
 #include "rotary.cuh"
 
@@ -49,7 +52,52 @@ __global__ void rotary_kernel(float* __restrict__ buf, const int* __restrict__ t
   }
 }
 
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_act_kernel(T* __restrict__ out, const T* __restrict__ gu, const T* __restrict__ h,
+                 const T* __restrict__ w_s, const int* __restrict__ tok_req, int ff, int width,
+                 int act) {
+  __shared__ float s_part[8];
+  const int t = blockIdx.x;
+  if (tok_req && tok_req[t] < 0) return;
+  float scale = 1.0f;
+  if (w_s) {
+    float dot = 0.f;
+    for (int k = threadIdx.x; k < width; k += 256)
+      dot = fmaf(to_f(h[(size_t)t * width + k]), to_f(w_s[k]), dot);
+    dot = warp_sum(dot);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = dot;
+    __syncthreads();
+    float z = 0.f;
+    for (int i = 0; i < 8; ++i) z += s_part[i];
+    scale = 1.0f / (1.0f + expf(-z));
+  }
+  const T* row = gu + (size_t)t * 2 * ff;
+  for (int f = threadIdx.x; f < ff; f += 256)
+    out[(size_t)t * ff + f] = from_f<T>(apply_act(to_f(row[f]), act) * to_f(row[ff + f]) * scale);
+}
+
 }  // namespace hs
+
+HS_EXPORT int hs_gated_act(void* out, const void* gu, const void* h, const void* w_s,
+                           const int* tok_req, int n_tokens, int ff, int width, int act,
+                           int dtype, void* stream) {
+  if (!out || !gu || (w_s && !h)) return HS_ERR_ARGUMENT;
+  if (ff <= 0 || act < HS_ACT_NONE || act > HS_ACT_LAST) return HS_ERR_UNSUPPORTED;
+  if (n_tokens <= 0) return HS_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == HS_DT_F32)
+    hs::gated_act_kernel<float><<<n_tokens, 256, 0, st>>>(
+        (float*)out, (const float*)gu, (const float*)h, (const float*)w_s, tok_req, ff, width, act);
+  else if (dtype == HS_DT_BF16)
+    hs::gated_act_kernel<__nv_bfloat16><<<n_tokens, 256, 0, st>>>(
+        (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, (const __nv_bfloat16*)h,
+        (const __nv_bfloat16*)w_s, tok_req, ff, width, act);
+  else
+    return HS_ERR_UNSUPPORTED;
+  HS_LAUNCH_CHECK();
+  return HS_OK;
+}
 
 HS_EXPORT int hs_dyt_norm(void* out, const float* x, const float* w, const float* b,
                           const int* rows, int n_rows, int width, float alpha, int out_dtype,

@@ -20,7 +20,8 @@ import torch
 
 from . import build as _build
 
-ACTIVATIONS = {"none": 0, "gelu_tanh": 1, "gelu_erf": 2}
+ACTIVATIONS = {"none": 0, "gelu_tanh": 1, "gelu_erf": 2, "relu2": 3, "silu": 4}
+EXPERT_ACTIVATIONS = {"clamped": 0, "silu": 1}
 _DT = {torch.float32: 0, torch.bfloat16: 1}
 
 
@@ -197,7 +198,16 @@ def _declare(lib) -> None:
         "hs_delta_recurrence": [P] * 10 + [I] * 8 + [P],
         "hs_delta_finish": [P, P, P, P, P, P, I, F, I, I, I, I, I, I, I, I, P, P],
         "hs_moe_route": [P, P, P, P, P, I, I, I, I, I, I, I, P, P],
-        "hs_moe_experts": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, F, I, P, P, P],
+        "hs_moe_experts": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, F, I, I, P, P, P],
+        "hs_moe_route_top": [P, P, P, P, P, P, I, I, I, I, I, P, P],
+        "hs_rms_norm": [P, P, P, P, I, I, F, I, P, I, I, I, P],
+        "hs_rms_norm_add": [P, P, P, P, P, P, F, P, I, I, F, F, I, P],
+        "hs_cast_rows": [P, P, ctypes.c_longlong, P],
+        "hs_gated_act": [P, P, P, P, P, I, I, I, I, I, P],
+        "hs_qk_prepare": [P, P, P, P, P, P, P, P, I, I, I, I, I, F, I, I, I, I, I, I, I, I, P, P],
+        "hs_biased_attention": [P, P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, I, F, F, I, I,
+                                I, P, P],
+        "hs_lightning_recurrence": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P],
         "hs_moe_sorted_scratch": [I, I, I, I, I, I, P, P],
         "hs_sample": [P, P, P, P, P, P, P, I, I, P, P, P, P],
     }
@@ -1191,9 +1201,11 @@ class CudaOps:
                                      keep, _DT[h.dtype], _ptr(z), self._stream()),
                f"moe_route(experts={E},top={top},groups={n_groups},keep={keep})")
 
-    def moe_experts(self, x, y, h, w_gate, w_up, w_down, sel_idx, sel_w, tok_req, *, limit):
+    def moe_experts(self, x, y, h, w_gate, w_up, w_down, sel_idx, sel_w, tok_req, *, limit,
+                    act="clamped"):
         """x += sum over a token's chosen experts of weight * W_down act(W_gate h, W_up h) with
-        act(g, u) = min(g, limit) * sigmoid(1.702 min(g, limit)) * (clamp(u, +-limit) + 1).
+        act(g, u) = min(g, limit) * sigmoid(1.702 min(g, limit)) * (clamp(u, +-limit) + 1)
+        (``act="clamped"``) or silu(g) * u (``act="silu"``, no limit).
         Expert matrices stacked as stored: gate / up [E, ff, width], down [E, width, ff]; ``y``
         is float32 scratch [T * top, ff].  Many pairs in bfloat16 are sorted by expert on the
         device and run as tiles on the tensor cores; few pairs, and float32, as one
@@ -1224,9 +1236,224 @@ class CudaOps:
         self.launches += 4 if ints is not None else 2
         _check(self.lib.hs_moe_experts(_ptr(x), _ptr(y), _ptr(h), _ptr(w_gate), _ptr(w_up),
                                        _ptr(w_down), _ptr(sel_idx), _ptr(sel_w), _ptr(tok_req),
-                                       T, width, ff, top, E, float(limit), _DT[h.dtype],
+                                       T, width, ff, top, E, float(limit),
+                                       EXPERT_ACTIVATIONS[act], _DT[h.dtype],
                                        _ptr(ints), _ptr(rows), self._stream()),
                f"moe_experts(ff={ff})")
+
+    def moe_route_top(self, sel_idx, sel_w, h, w_router, bias, tok_req, *, top, z=None):
+        """Per token: float32 logits ``W_r h + bias``, the ``top`` largest (the lower index wins
+        a tie), weights = softmax over the chosen logits alone.  ``z`` [T, experts] float32, if
+        given, holds ``W_r h`` (formed as one matrix product over the step)."""
+        _want(sel_idx, "sel_idx", torch.int32, 2)
+        _want(sel_w, "sel_w", torch.float32, 2)
+        _want(h, "h", _FLOATS, 2)
+        _want(w_router, "w_router", torch.float32, 2)
+        E, width = w_router.shape
+        if bias is not None:
+            _want(bias, "bias", torch.float32, 1)
+            if bias.shape[0] != E:
+                raise KernelError("moe_route_top: one bias per expert")
+        if h.shape[1] != width or sel_idx.shape[1] != top or sel_w.shape[1] != top:
+            raise KernelError("moe_route_top: shapes do not fit")
+        self.launches += 1
+        _check(self.lib.hs_moe_route_top(_ptr(sel_idx), _ptr(sel_w), _ptr(h), _ptr(w_router),
+                                         _ptr(bias), _ptr(tok_req), sel_idx.shape[0], width, E,
+                                         top, _DT[h.dtype], _ptr(z), self._stream()),
+               f"moe_route_top(experts={E},top={top})")
+
+    def gated_act(self, out, gu, h=None, w_s=None, tok_req=None, act="silu"):
+        """out[t, f] = act(gu[t, f]) * gu[t, ff + f] (* sigmoid(h[t] . w_s), one number per
+        token, when ``w_s`` is given): the middle of a gated feed-forward whose gate and up
+        projections came as one product."""
+        _want(out, "out", _FLOATS, 2)
+        _want(gu, "gu", out.dtype, 2)
+        T, ff = out.shape
+        if gu.shape[1] != 2 * ff or gu.shape[0] < T:
+            raise KernelError("gated_act: gu is [T, 2 * ff]")
+        width = 0
+        if w_s is not None:
+            _want(h, "h", out.dtype, 2)
+            _want(w_s, "w_s", out.dtype, 1)
+            width = h.shape[1]
+            if w_s.shape[0] != width or h.shape[0] < T:
+                raise KernelError("gated_act: h and w_s do not fit")
+        if act not in ACTIVATIONS:
+            raise KernelError(f"gated_act: unknown activation {act!r}")
+        self.launches += 1
+        _check(self.lib.hs_gated_act(_ptr(out), _ptr(gu), _ptr(h), _ptr(w_s), _ptr(tok_req), T, ff,
+                                     width, ACTIVATIONS[act], _DT[out.dtype], self._stream()),
+               "gated_act")
+
+    # -- root-mean-square norms ---------------------------------------------------------
+    def rms_norm(self, out, x, weight, eps, rows=None, one_plus=False, gate=None, gate_offset=0):
+        """out[i] = x[r] / sqrt(mean(x[r]^2) + eps) * weight (r = rows[i] or i; ``one_plus``:
+        times 1 + weight); with ``gate`` (float32 [T, *]) also times
+        sigmoid(gate[r, gate_offset + e]) per element."""
+        _want(out, "out", _FLOATS, 2)
+        _want(x, "x", torch.float32, 2)
+        _want(weight, "weight", torch.float32, 1)
+        n, width = out.shape
+        if x.shape[1] != width or weight.shape[0] != width:
+            raise KernelError("rms_norm: widths of out, x, weight differ")
+        if rows is not None:
+            _want(rows, "rows", torch.int32, 1)
+            if rows.shape[0] < n:
+                raise KernelError("rms_norm: fewer row indices than output rows")
+        elif x.shape[0] < n:
+            raise KernelError("rms_norm: x has fewer rows than out")
+        g_stride = 0
+        if gate is not None:
+            _want(gate, "gate", torch.float32, 2)
+            g_stride = gate.shape[1]
+            if gate_offset + width > g_stride or gate.shape[0] < x.shape[0]:
+                raise KernelError("rms_norm: the gate columns exceed the gate's row")
+        self.launches += 1
+        _check(self.lib.hs_rms_norm(_ptr(out), _ptr(x), _ptr(weight), _ptr(rows), n, width,
+                                    float(eps), int(bool(one_plus)), _ptr(gate), int(gate_offset),
+                                    g_stride, _DT[out.dtype], self._stream()),
+               f"rms_norm(width={width})")
+
+    def rms_norm_add(self, x, a, weight, eps, h=None, b=None, wa=None, wb=None, mix=0.5,
+                     eps_in=None):
+        """The norm of a sublayer's output added into the stream: with y = a, or, given a second
+        input, y = mix * (rms(a) * wa + rms(b) * wb) (those two norms with ``eps_in``, by
+        default ``eps``):  x += rms(y) * weight, or x += y when ``weight`` is None.  ``h`` (of
+        the compute type), if given, receives a copy of the new x."""
+        _want(x, "x", torch.float32, 2)
+        _want(a, "a", torch.float32, 2)
+        n, width = x.shape
+        if weight is not None:
+            _want(weight, "weight", torch.float32, 1)
+        if a.shape[0] < n or a.shape[1] != width or \
+                (weight is not None and weight.shape[0] != width):
+            raise KernelError("rms_norm_add: shapes do not fit")
+        if b is not None:
+            _want(b, "b", torch.float32, 2)
+            _want(wa, "wa", torch.float32, 1)
+            _want(wb, "wb", torch.float32, 1)
+            if b.shape[0] < n or b.shape[1] != width or wa.shape[0] != width \
+                    or wb.shape[0] != width:
+                raise KernelError("rms_norm_add: the second input does not fit")
+        if h is not None:
+            _want(h, "h", _FLOATS, 2)
+            if tuple(h.shape) != (n, width):
+                raise KernelError("rms_norm_add: h has another shape than x")
+        self.launches += 1
+        _check(self.lib.hs_rms_norm_add(_ptr(x), _ptr(h), _ptr(a), _ptr(wa), _ptr(b), _ptr(wb),
+                                        float(mix), _ptr(weight), n, width,
+                                        float(eps if eps_in is None else eps_in), float(eps),
+                                        _DT[h.dtype] if h is not None else 0, self._stream()),
+               f"rms_norm_add(width={width})")
+
+    def cast_rows(self, out, x):
+        """out = x (float32) rounded to bfloat16, elementwise."""
+        _want(out, "out", torch.bfloat16)
+        _want(x, "x", torch.float32)
+        if out.numel() != x.numel():
+            raise KernelError("cast_rows: sizes differ")
+        self.launches += 1
+        _check(self.lib.hs_cast_rows(_ptr(out), _ptr(x), x.numel(), self._stream()), "cast_rows")
+
+    # -- attention with a distance bias, a score cap and a chunked mask --------------------
+    def qk_prepare(self, q_out, pool, proj, wq, wk, table, tok_pos, tok_req, *, q_off, k_off,
+                   v_off, eps, writes, n_heads, n_kv_heads, head_dim, page_size, status):
+        """From float32 projection rows: queries RMS-normed over all ``n_heads * head_dim``
+        entries at once (times ``wq``; None: as they are) into ``q_out``; keys normed likewise
+        over ``n_kv_heads * head_dim`` (``wk``) into plane 0 of the token's page, values
+        (columns at ``v_off``, or the un-normed keys when ``v_off`` is None) into plane 1.
+        ``pool`` is [pages, 2, kv_heads, page_size, head_dim]."""
+        _want(proj, "proj", torch.float32, 2)
+        _want(q_out, "q_out", _FLOATS, 2)
+        _want(pool, "pool", q_out.dtype)
+        _want(table, "table", torch.int32, 2)
+        n = q_out.shape[0]
+        qw, kw = n_heads * head_dim, n_kv_heads * head_dim
+        for t, nm, width in ((wq, "wq", qw), (wk, "wk", kw)):
+            if t is not None:
+                _want(t, nm, torch.float32, 1)
+                if t.shape[0] != width:
+                    raise KernelError(f"qk_prepare: {nm} has {t.shape[0]} entries, not {width}")
+        if q_out.shape[1] != qw or proj.shape[0] < n or tok_pos.shape[0] < n or tok_req.shape[0] < n:
+            raise KernelError("qk_prepare: rows do not fit")
+        vo = -1 if v_off is None else int(v_off)
+        if max(q_off + qw, k_off + kw, vo + kw if vo >= 0 else 0) > proj.shape[1]:
+            raise KernelError("qk_prepare: the columns exceed the projection's row")
+        per_page = 2 * n_kv_heads * page_size * head_dim
+        if pool.numel() % per_page:
+            raise KernelError("qk_prepare: the pool does not fit the sizes")
+        self.launches += 1
+        _check(self.lib.hs_qk_prepare(_ptr(q_out), _ptr(pool), _ptr(proj), _ptr(wq), _ptr(wk),
+                                      _ptr(table), _ptr(tok_pos), _ptr(tok_req), n, proj.shape[1],
+                                      int(q_off), int(k_off), vo, float(eps), int(bool(writes)),
+                                      n_heads, n_kv_heads, head_dim, page_size,
+                                      pool.numel() // per_page, table.shape[1], _DT[q_out.dtype],
+                                      _ptr(status), self._stream()),
+               f"qk_prepare(head_dim={head_dim})")
+
+    def biased_attention(self, out, q, pool, table, tok_pos, tok_req, *, bias, gate, gate_offset,
+                         n_heads, n_kv_heads, head_dim, page_size, scale, cap, chunk, window,
+                         status):
+        """Causal softmax attention over the pages with score = cap * tanh(q . k * scale / cap)
+        + bias[h, i - j] (``cap`` 0: none; ``bias`` float32 [heads, distances] or None), keys
+        restricted to the query's chunk of ``chunk`` positions (0: none) and to the last
+        ``window`` (0: all); head h's output is multiplied by sigmoid(gate[t, gate_offset + h])
+        when ``gate`` (float32 [T, *]) is given."""
+        _want(out, "out", _FLOATS, 2)
+        _want(q, "q", out.dtype, 2)
+        _want(pool, "pool", out.dtype)
+        _want(table, "table", torch.int32, 2)
+        n = out.shape[0]
+        if out.shape[1] != n_heads * head_dim or q.shape[1] != n_heads * head_dim or q.shape[0] < n:
+            raise KernelError("biased_attention: out / q are [T, n_heads * head_dim]")
+        n_dist = 0
+        if bias is not None:
+            _want(bias, "bias", torch.float32, 2)
+            if bias.shape[0] != n_heads:
+                raise KernelError("biased_attention: one row of biases per head")
+            n_dist = bias.shape[1]
+        g_stride = 0
+        if gate is not None:
+            _want(gate, "gate", torch.float32, 2)
+            g_stride = gate.shape[1]
+            if gate_offset + n_heads > g_stride or gate.shape[0] < n:
+                raise KernelError("biased_attention: the gate columns exceed the gate's row")
+        per_page = 2 * n_kv_heads * page_size * head_dim
+        if pool.numel() % per_page:
+            raise KernelError("biased_attention: the pool does not fit the sizes")
+        self.launches += 1
+        _check(self.lib.hs_biased_attention(
+            _ptr(out), _ptr(q), _ptr(pool), _ptr(table), _ptr(tok_pos), _ptr(tok_req), _ptr(bias),
+            n_dist, _ptr(gate), int(gate_offset), g_stride, n, n_heads, n_kv_heads, head_dim,
+            page_size, pool.numel() // per_page, table.shape[1], float(scale), float(cap),
+            int(chunk), int(window), _DT[out.dtype], _ptr(status), self._stream()),
+            f"biased_attention(head_dim={head_dim})")
+
+    # -- linear attention with a decay per head ---------------------------------------------
+    def lightning_recurrence(self, o, state, proj, decay, req_start, req_len, req_slot, *, q_off,
+                             k_off, v_off, heads, dim, vdim, act="silu"):
+        """Per request and head, token after token on the float32 state S [dim, vdim] of the
+        request's slot: S <- decay[h] S + k v^T; o = S^T q, with q, k, v = act(columns of the
+        float32 projection rows ``proj``), laid out head by head from ``q_off``, ``k_off``,
+        ``v_off``.  ``o`` is float32 [T, heads * vdim]."""
+        _want(o, "o", torch.float32, 2)
+        _want(proj, "proj", torch.float32, 2)
+        _want(state, "state", torch.float32)
+        _want(decay, "decay", torch.float32, 1)
+        if decay.shape[0] != heads or o.shape[1] != heads * vdim:
+            raise KernelError("lightning_recurrence: decay / o do not fit the heads")
+        if state[0].numel() != heads * dim * vdim:
+            raise KernelError("lightning_recurrence: the state does not fit the sizes")
+        if max(q_off + heads * dim, k_off + heads * dim, v_off + heads * vdim) > proj.shape[1]:
+            raise KernelError("lightning_recurrence: the columns exceed the projection's row")
+        if act not in ("none", "silu"):
+            raise KernelError(f"lightning_recurrence: activation {act!r} not taken")
+        self.launches += 1
+        _check(self.lib.hs_lightning_recurrence(
+            _ptr(o), _ptr(state), _ptr(proj), _ptr(decay), _ptr(req_start), _ptr(req_len),
+            _ptr(req_slot), req_start.shape[0], proj.shape[1], int(q_off), int(k_off), int(v_off),
+            heads, dim, vdim, ACTIVATIONS[act], self._stream()),
+            f"lightning_recurrence(dim={dim},vdim={vdim})")
 
     # -- sampling ---------------------------------------------------------------
     def argmax(self, out, logits):

@@ -24,18 +24,19 @@ class Block:
     entry or a state slot (a :class:`LayerCall` addresses one of each)."""
 
     slots: Mapping[str, str] = {}          # part name -> family ("mixer", "feed_forward", "norm")
+    optional: tuple[str, ...] = ()         # slots a layer may leave out (the attribute is None)
 
     def __init__(self, spec: LayerSpec):
         self.spec = spec
-        missing = [n for n in self.slots if n not in spec.parts]
+        missing = [n for n in self.slots if n not in spec.parts and n not in self.optional]
         extra = [n for n in spec.parts if n not in self.slots]
         if missing or extra:
             raise ValueError(f"arrangement {spec.arrangement!r} has the parts "
                              f"{sorted(self.slots)}; missing {missing}, unknown {extra}")
         self.named = {name: build_part(family, spec.parts[name])
-                      for name, family in self.slots.items()}
-        for name, part in self.named.items():
-            setattr(self, name, part)
+                      for name, family in self.slots.items() if name in spec.parts}
+        for name in self.slots:
+            setattr(self, name, self.named.get(name))
         holders = [p for n, p in self.named.items() if self.slots[n] == "mixer"
                    and (p.cache_request() is not None or p.state_shape() is not None)]
         if len(holders) > 1:
@@ -84,8 +85,63 @@ class ParallelBlock(Block):
         self.feed_forward.forward(ctx, h, x)
 
 
+class OutputNormBlock(Block):
+    """Norms behind the sublayers, which read the stream itself:
+
+        x += norm1(mixer(x));  x += norm2(feed_forward(x))
+
+    The sublayers' input ``h`` is the stream in the compute type (the stream itself in
+    float32).  A sublayer's output goes to a float32 block of its own: parts that can write
+    one (``writes_fresh``) are called with ``fresh=True`` and may hand back a deferred output
+    the norm forms on the way (:class:`hetero_serve_b200.parts.rms_norm.NormedPair`); for the
+    others the block is zeroed and they add into it as they add into a stream.  The norms
+    must offer ``add_normed``.  A layer may leave ``norm2`` and ``feed_forward`` out (both or
+    neither): it then ends after the mixer."""
+
+    slots = {"norm1": "norm", "mixer": "mixer", "norm2": "norm", "feed_forward": "feed_forward"}
+    optional = ("norm2", "feed_forward")
+    keeps_stream_copy = True
+
+    def __init__(self, spec: LayerSpec):
+        super().__init__(spec)
+        if (self.norm2 is None) != (self.feed_forward is None):
+            raise ValueError("arrangement 'output_norm': norm2 and feed_forward come together")
+        for name, part in self.named.items():
+            if self.slots[name] == "norm" and not hasattr(part, "add_normed"):
+                raise ValueError(f"arrangement 'output_norm': {name} of kind {part.kind!r} "
+                                 f"cannot be applied to a sublayer's output (no add_normed)")
+        self.has_ff = self.feed_forward is not None
+
+    @staticmethod
+    def _run(part, ctx, h, y, *more):
+        if getattr(part, "writes_fresh", False):
+            out = part.forward(ctx, h, y, *more, fresh=True)
+            return y if out is None else out
+        y.zero_()
+        part.forward(ctx, h, y, *more)
+        return y
+
+    def forward(self, ctx, x, cache):
+        T, W = x.shape
+        low = ctx.dtype != torch.float32
+        if low:
+            h = ctx.buffer("stream_copy", (T, W), ctx.dtype)
+            if not getattr(ctx, "stream_copy_fresh", False):
+                ctx.ops.cast_rows(h, x)
+        else:
+            h = x
+        y = ctx.buffer("sublayer_out", (T, W), torch.float32)
+        out = self._run(self.mixer, ctx, h, y, cache)
+        self.norm1.add_normed(ctx, x, out, h=h if low else None)
+        if self.has_ff:
+            out = self._run(self.feed_forward, ctx, h, y)
+            self.norm2.add_normed(ctx, x, out, h=h if low else None)
+        ctx.stream_copy_fresh = low
+
+
 _ARRANGEMENTS: dict[str, Callable[[LayerSpec], Block]] = {"pre_norm": PreNormBlock,
-                                                          "parallel": ParallelBlock}
+                                                          "parallel": ParallelBlock,
+                                                          "output_norm": OutputNormBlock}
 
 
 def register_arrangement(name: str, factory: Callable[[LayerSpec], Block], *, replace=False):
@@ -217,10 +273,14 @@ class Model:
         x = ctx.buffer("residual", (T, spec.width), torch.float32)
         ctx.position = self.position          # mixers ask it whether it acts on queries and keys
         self.embedding.forward(ctx, x, self.position)
+        ctx.stream_copy_fresh = False         # no copy of the stream in the compute type yet
         for idx, call in enumerate(self.schedule):
             ctx.call_index = idx
             cache = ctx.cache_view(call) if call.cache in self.entry_location else None
-            self.blocks[call.layer].forward(ctx, x, cache)
+            block = self.blocks[call.layer]
+            block.forward(ctx, x, cache)
+            if not getattr(block, "keeps_stream_copy", False):
+                ctx.stream_copy_fresh = False
         ctx.call_index = None
         W = ctx.n_logit_rows
         if W == 0:

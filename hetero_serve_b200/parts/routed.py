@@ -11,31 +11,60 @@ Their weights are their scores divided by the scores' sum (+ 1e-20).  An expert 
 and the layer adds the weighted sum of the chosen experts' outputs into the stream.  The
 experts' matrices are stacked once at binding so that one kernel serves all experts.
 Routing happens on the device; cache and scheduler know nothing of it.
+
+A second rule (``scoring="softmax_top"``): z = W_r h + b_r in float32, the ``top`` largest
+logits are chosen (the lower index wins a tie) and weighted by the softmax over the chosen
+logits alone; and a second expert (``activation="silu"``): y = silu(W_gate h) * (W_up h).
+``shared`` names a feed-forward (a :class:`PartSpec`) that runs for every token beside the
+experts and is added to their sum.
 """
 
 from __future__ import annotations
 
 import torch
 
-from .base import FeedForward, TensorRequest, register_feed_forward
+from .base import FeedForward, TensorRequest, build_part, register_feed_forward
+
+SCORINGS = ("sigmoid_groups", "softmax_top")
 
 
 class RoutedExperts(FeedForward):
-    def __init__(self, *, width: int, ff: int, experts: int, top: int, groups: int, keep: int,
-                 limit: float, router: str, expert_prefix: str):
-        if experts % groups:
-            raise ValueError(f"{experts} experts do not form {groups} equal groups")
-        if not 0 < keep <= groups or not 0 < top <= keep * (experts // groups):
-            raise ValueError("top experts must fit into the kept groups")
+    writes_fresh = True
+
+    def __init__(self, *, width: int, ff: int, experts: int, top: int, router: str,
+                 expert_prefix: str, groups: int = 1, keep: int = 1, limit: float = 0.0,
+                 scoring: str = "sigmoid_groups", activation: str = "clamped",
+                 router_bias: str | None = None, shared=None):
+        if scoring not in SCORINGS:
+            raise ValueError(f"unknown scoring {scoring!r}; known: {SCORINGS}")
+        if activation not in ("clamped", "silu"):
+            raise ValueError(f"unknown expert activation {activation!r}")
+        if scoring == "sigmoid_groups":
+            if experts % groups:
+                raise ValueError(f"{experts} experts do not form {groups} equal groups")
+            if not 0 < keep <= groups or not 0 < top <= keep * (experts // groups):
+                raise ValueError("top experts must fit into the kept groups")
+            if router_bias is not None:
+                raise ValueError("the grouped sigmoid rule takes no router bias")
+        elif not 0 < top <= experts:
+            raise ValueError(f"{top} chosen experts of {experts}")
         self.width, self.ff, self.E, self.top = width, ff, experts, top
         self.groups, self.keep, self.limit = groups, keep, float(limit)
-        self.router_name, self.prefix = router, expert_prefix
+        self.scoring, self.activation = scoring, activation
+        self.router_name, self.bias_name, self.prefix = router, router_bias, expert_prefix
+        self.shared = build_part("feed_forward", shared) if shared is not None else None
+        if self.shared is not None:
+            self.capturable = self.shared.capturable
 
     def _expert(self, e: int, which: str) -> str:
         return f"{self.prefix}{e}.{which}"
 
     def tensor_requests(self):
         req = {self.router_name: TensorRequest((self.E, self.width), "float32")}
+        if self.bias_name:
+            req[self.bias_name] = TensorRequest((self.E,), "vector")
+        if self.shared is not None:
+            req.update(self.shared.tensor_requests())
         for e in range(self.E):
             req[self._expert(e, "gate")] = TensorRequest((self.ff, self.width), "matrix")
             req[self._expert(e, "up")] = TensorRequest((self.ff, self.width), "matrix")
@@ -44,6 +73,9 @@ class RoutedExperts(FeedForward):
 
     def bind(self, tensors):
         self.w_router = tensors[self.router_name]
+        self.b_router = tensors[self.bias_name] if self.bias_name else None
+        if self.shared is not None:
+            self.shared.bind({n: tensors[n] for n in self.shared.tensor_requests()})
         # prompt portions in bfloat16 form the logits as one product on the tensor cores (exact
         # products, float32 sums) when the router's values are bfloat16 numbers to begin with
         self.w_router_lp = None
@@ -57,19 +89,33 @@ class RoutedExperts(FeedForward):
                                 for e in range(self.E)]).contiguous()
         self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
 
-    def forward(self, ctx, h, x):
+    def forward(self, ctx, h, x, fresh=False):
         ops, T = ctx.ops, h.shape[0]
+        if self.shared is not None:          # first: with ``fresh`` it is what opens x
+            if fresh and getattr(self.shared, "writes_fresh", False):
+                self.shared.forward(ctx, h, x, fresh=True)
+            else:
+                if fresh:
+                    x.zero_()
+                self.shared.forward(ctx, h, x)
+        elif fresh:
+            x.zero_()
         idx = ctx.buffer("route_idx", (T, self.top), torch.int32)
         wts = ctx.buffer("route_w", (T, self.top), torch.float32)
         z = None
         if self.w_router_lp is not None and T >= 64:
             z = ctx.buffer("route_z", (T, self.E), torch.float32)
             ops.linear(z, h, self.w_router_lp)
-        ops.moe_route(idx, wts, h, self.w_router, ctx.tok_req, top=self.top,
-                      n_groups=self.groups, keep=self.keep, z=z)
+        if self.scoring == "softmax_top":
+            ops.moe_route_top(idx, wts, h, self.w_router, self.b_router, ctx.tok_req,
+                              top=self.top, z=z)
+        else:
+            ops.moe_route(idx, wts, h, self.w_router, ctx.tok_req, top=self.top,
+                          n_groups=self.groups, keep=self.keep, z=z)
         y = ctx.buffer("expert_act", (T * self.top, self.ff), torch.float32)
+        more = {"act": self.activation} if self.activation != "clamped" else {}
         ops.moe_experts(x, y, h, self.w_gate, self.w_up, self.w_down, idx, wts, ctx.tok_req,
-                        limit=self.limit)
+                        limit=self.limit, **more)
 
 
 class NoFeedForward(FeedForward):

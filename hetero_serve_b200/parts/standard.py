@@ -213,19 +213,60 @@ class DenseFeedForward(FeedForward):
         self.b_out = tensors[ob] if ob else None
 
     takes_norm = True
+    writes_fresh = True       # with fresh=True the result is written to x, not added into it
 
     def fused_decode_params(self):
+        if self.act not in ("none", "gelu_tanh", "gelu_erf"):
+            return None
         return dict(w_in=self.w_in, b_in=self.b_in, w_out=self.w_out, b_out=self.b_out,
                     width=self.width, inner=self.inner, activation=self.act)
 
-    def forward(self, ctx, h, x, norm=None):
+    def forward(self, ctx, h, x, norm=None, fresh=False):
         T = h.shape[0]
         u = ctx.buffer("ff_inner", (T, self.inner), ctx.dtype)
         if norm is not None:
             norm.linear(ctx, u, h, x, self.w_in, self.b_in, act=self.act)
         else:
             ctx.ops.linear(u, h, self.w_in, self.b_in, act=self.act)
-        ctx.ops.linear(x, u, self.w_out, self.b_out, residual=x)
+        ctx.ops.linear(x, u, self.w_out, self.b_out, residual=None if fresh else x)
+
+
+class GatedFeedForward(FeedForward):
+    """x += W_down (act(W_gate h) * (W_up h)) * s, with s = sigmoid(w_s . h), one number per
+    token, when a token gate is named (else 1).  Gate and up are one product; the token gate
+    is applied to the inner activations, which the down projection then carries through."""
+
+    writes_fresh = True
+
+    def __init__(self, *, width: int, inner: int, activation: str, gate_weight: str,
+                 up_weight: str, down_weight: str, token_gate: str | None = None):
+        if activation not in ACTIVATIONS:
+            raise ValueError(f"unknown activation {activation!r}; known: {sorted(ACTIVATIONS)}")
+        self.width, self.inner, self.act = width, inner, activation
+        self.names = (gate_weight, up_weight, down_weight, token_gate)
+
+    def tensor_requests(self):
+        gw, uw, dw, tg = self.names
+        req = {gw: TensorRequest((self.inner, self.width), "matrix"),
+               uw: TensorRequest((self.inner, self.width), "matrix"),
+               dw: TensorRequest((self.width, self.inner), "matrix")}
+        if tg:
+            req[tg] = TensorRequest((1, self.width), "matrix")
+        return req
+
+    def bind(self, tensors):
+        gw, uw, dw, tg = self.names
+        self.w_gu = torch.cat([tensors[gw], tensors[uw]]).contiguous()
+        self.w_down = tensors[dw]
+        self.w_s = tensors[tg].reshape(-1).contiguous() if tg else None
+
+    def forward(self, ctx, h, x, fresh=False):
+        T = h.shape[0]
+        gu = ctx.buffer("gated_gu", (T, 2 * self.inner), ctx.dtype)
+        ctx.ops.linear(gu, h, self.w_gu)
+        u = ctx.buffer("gated_inner", (T, self.inner), ctx.dtype)
+        ctx.ops.gated_act(u, gu, h, self.w_s, ctx.tok_req, act=self.act)
+        ctx.ops.linear(x, u, self.w_down, None, residual=None if fresh else x)
 
 
 class LinearHead(Head):
@@ -270,4 +311,5 @@ register_embedding("token_table", TokenEmbedding)
 register_norm("layernorm", LayerNorm)
 register_mixer("causal_attention", CausalAttention)
 register_feed_forward("dense", DenseFeedForward)
+register_feed_forward("gated", GatedFeedForward)
 register_head("linear", LinearHead)

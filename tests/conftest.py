@@ -106,3 +106,14 @@ def pedorax_case(request, pedorax_cases):
 def pedorax_one_kind(request, pedorax_cases):
     """Models with layers of one kind only: no page group at all, or no state in use."""
     return pedorax_cases[request.param]
+
+
+@pytest.fixture(scope="session")
+def putelix_cases(tmp_path_factory):
+    import putelix_cases as uc
+    return uc.make_cases(tmp_path_factory)
+
+
+@pytest.fixture(params=["case_a", "case_b"])
+def putelix_case(request, putelix_cases):
+    return putelix_cases[request.param]

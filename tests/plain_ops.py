@@ -19,7 +19,8 @@ try:
 except ImportError:  # run as a top-level module
     from plain_gpt2 import gelu_erf, gelu_new, philox4x32, sample_token, uniform_for
 
-_ACT = {"none": lambda u: u, "gelu_tanh": gelu_new, "gelu_erf": gelu_erf}
+_ACT = {"none": lambda u: u, "gelu_tanh": gelu_new, "gelu_erf": gelu_erf,
+        "relu2": lambda u: torch.relu(u) ** 2, "silu": lambda u: u * torch.sigmoid(u)}
 
 
 class PlainOps:
@@ -295,8 +296,22 @@ class PlainOps:
             sel_idx[t] = idx.to(torch.int32)
             sel_w[t] = (s[idx] / (s[idx].sum() + 1e-20)).to(sel_w.dtype)
 
-    def moe_experts(self, x, y, h, w_gate, w_up, w_down, sel_idx, sel_w, tok_req, *, limit):
+    def moe_experts(self, x, y, h, w_gate, w_up, w_down, sel_idx, sel_w, tok_req, *, limit,
+                    act="clamped"):
         T, top = sel_idx.shape
+        if act == "silu":
+            for t in range(T):
+                if int(tok_req[t]) < 0:
+                    continue
+                hv = h[t].to(self.cd)
+                add = torch.zeros(x.shape[1], dtype=self.cd)
+                for k in range(top):
+                    e = int(sel_idx[t, k])
+                    g = w_gate[e].to(self.cd) @ hv
+                    inner = g * torch.sigmoid(g) * (w_up[e].to(self.cd) @ hv)
+                    add = add + sel_w[t, k].to(self.cd) * (w_down[e].to(self.cd) @ inner)
+                x[t] = (x[t].to(self.cd) + add).to(x.dtype)
+            return
         for t in range(T):
             if int(tok_req[t]) < 0:
                 continue
@@ -309,3 +324,126 @@ class PlainOps:
                 act = g * torch.sigmoid(1.702 * g) * (u + 1.0)
                 add = add + sel_w[t, k].to(self.cd) * (w_down[e].to(self.cd) @ act)
             x[t] = (x[t].to(self.cd) + add).to(x.dtype)
+
+    def moe_route_top(self, sel_idx, sel_w, h, w_router, bias, tok_req, *, top, z=None):
+        for t in range(sel_idx.shape[0]):
+            if int(tok_req[t]) < 0:
+                continue
+            logits = (w_router.to(self.cd) @ h[t].to(self.cd)) if z is None else z[t].to(self.cd)
+            if bias is not None:
+                logits = logits + bias.to(self.cd)
+            order = sorted(range(logits.shape[0]), key=lambda e: (-float(logits[e]), e))[:top]
+            idx = torch.tensor(order)
+            sel_idx[t] = idx.to(torch.int32)
+            sel_w[t] = torch.softmax(logits[idx], 0).to(sel_w.dtype)
+
+    def gated_act(self, out, gu, h=None, w_s=None, tok_req=None, act="silu"):
+        ff = out.shape[1]
+        v = gu.to(self.cd)
+        r = _ACT[act](v[:, :ff]) * v[:, ff:]
+        if w_s is not None:
+            r = r * torch.sigmoid(h.to(self.cd) @ w_s.to(self.cd))[:, None]
+        out.copy_(r.to(out.dtype))
+
+    # -- root-mean-square norms, attention with a distance bias, lightning attention ----------
+    def _rms(self, v, eps):
+        return v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps)
+
+    def rms_norm(self, out, x, weight, eps, rows=None, one_plus=False, gate=None, gate_offset=0):
+        n, width = out.shape
+        sel = rows[:n].long() if rows is not None else torch.arange(n)
+        w = weight.to(self.cd)
+        v = self._rms(x[sel].to(self.cd), eps) * ((1.0 + w) if one_plus else w)
+        if gate is not None:
+            v = v * torch.sigmoid(gate[sel, gate_offset:gate_offset + width].to(self.cd))
+        out.copy_(v.to(out.dtype))
+
+    def rms_norm_add(self, x, a, weight, eps, h=None, b=None, wa=None, wb=None, mix=0.5,
+                     eps_in=None):
+        n = x.shape[0]
+        y = a[:n].to(self.cd)
+        if b is not None:
+            e_in = eps if eps_in is None else eps_in
+            y = mix * (self._rms(y, e_in) * wa.to(self.cd)
+                       + self._rms(b[:n].to(self.cd), e_in) * wb.to(self.cd))
+        if weight is not None:
+            y = self._rms(y, eps) * weight.to(self.cd)
+        x.copy_((x.to(self.cd) + y).to(x.dtype))
+        if h is not None:
+            h.copy_(x.to(h.dtype))
+
+    def cast_rows(self, out, x):
+        out.copy_(x.to(out.dtype).view_as(out))
+
+    def qk_prepare(self, q_out, pool, proj, wq, wk, table, tok_pos, tok_req, *, q_off, k_off,
+                   v_off, eps, writes, n_heads, n_kv_heads, head_dim, page_size, status):
+        qw, kw = n_heads * head_dim, n_kv_heads * head_dim
+        pv = pool.view(-1, 2, n_kv_heads, page_size, head_dim)
+        for t in range(q_out.shape[0]):
+            r = int(tok_req[t])
+            if r < 0:
+                continue
+            row = proj[t].to(self.cd)
+            q, k = row[q_off:q_off + qw], row[k_off:k_off + kw]
+            v = k if v_off is None else row[v_off:v_off + kw]
+            if wq is not None:
+                q = self._rms(q, eps) * wq.to(self.cd)
+            kn = self._rms(k, eps) * wk.to(self.cd) if wk is not None else k
+            q_out[t] = q.to(q_out.dtype)
+            if not writes:
+                continue
+            p = int(tok_pos[t])
+            page = int(table[r, p // page_size])
+            pv[page, 0, :, p % page_size] = kn.view(n_kv_heads, head_dim).to(pool.dtype)
+            pv[page, 1, :, p % page_size] = v.view(n_kv_heads, head_dim).to(pool.dtype)
+
+    def biased_attention(self, out, q, pool, table, tok_pos, tok_req, *, bias, gate, gate_offset,
+                         n_heads, n_kv_heads, head_dim, page_size, scale, cap, chunk, window,
+                         status):
+        pv = pool.view(-1, 2, n_kv_heads, page_size, head_dim)
+        group = n_heads // n_kv_heads
+        for t in range(out.shape[0]):
+            r = int(tok_req[t])
+            if r < 0:
+                continue
+            i = int(tok_pos[t])
+            lo = i // chunk * chunk if chunk > 0 else 0
+            if window > 0:
+                lo = max(lo, i - window + 1)
+            js = list(range(lo, i + 1))
+            pages = [int(table[r, j // page_size]) for j in js]
+            slots = [j % page_size for j in js]
+            qt = q[t].to(self.cd).view(n_heads, head_dim)
+            for hd in range(n_heads):
+                g = hd // group
+                keys = torch.stack([pv[pg, 0, g, sl] for pg, sl in zip(pages, slots)]).to(self.cd)
+                vals = torch.stack([pv[pg, 1, g, sl] for pg, sl in zip(pages, slots)]).to(self.cd)
+                s = (keys @ qt[hd]) * scale
+                if cap > 0:
+                    s = cap * torch.tanh(s / cap)
+                if bias is not None:
+                    dist = torch.tensor([min(i - j, bias.shape[1] - 1) for j in js])
+                    s = s + bias[hd, dist].to(self.cd)
+                o = torch.softmax(s, 0) @ vals
+                if gate is not None:
+                    o = o * torch.sigmoid(gate[t, gate_offset + hd].to(self.cd))
+                out[t, hd * head_dim:(hd + 1) * head_dim] = o.to(out.dtype)
+
+    def lightning_recurrence(self, o, state, proj, decay, req_start, req_len, req_slot, *, q_off,
+                             k_off, v_off, heads, dim, vdim, act="silu"):
+        f = _ACT[act]
+        for r in range(req_start.shape[0]):
+            n = int(req_len[r])
+            if n <= 0:
+                continue
+            t0, slot = int(req_start[r]), int(req_slot[r])
+            S = state[slot].to(self.cd).view(heads, dim, vdim).clone()
+            for t in range(t0, t0 + n):
+                row = proj[t].to(self.cd)
+                q = f(row[q_off:q_off + heads * dim]).view(heads, dim)
+                k = f(row[k_off:k_off + heads * dim]).view(heads, dim)
+                v = f(row[v_off:v_off + heads * vdim]).view(heads, vdim)
+                for hd in range(heads):
+                    S[hd] = decay[hd].to(self.cd) * S[hd] + torch.outer(k[hd], v[hd])
+                    o[t, hd * vdim:(hd + 1) * vdim] = (S[hd].T @ q[hd]).to(o.dtype)
+            state[slot] = S.reshape(-1).to(state.dtype)
