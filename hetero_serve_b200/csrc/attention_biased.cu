@@ -18,6 +18,8 @@
 // multiply-adds over d), an online softmax in float32, lane e accumulates output entries
 // e, e + 32, ...  The first step starts at the first visible key, so the order of every sum
 // depends on the positions alone, never on the batch, the cut of the prompt or the pages.
+// This kernel serves float32, single tokens (decoding) and every size the tile kernel
+// (attention_biased_mma.cu) does not take.
 #include "common.cuh"
 
 namespace hs {
@@ -125,12 +127,17 @@ biased_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
                         const int* __restrict__ table, const int* __restrict__ tok_pos,
                         const int* __restrict__ tok_req, const float* __restrict__ bias,
                         const float* __restrict__ gate, int g_off, int g_stride, int n_tokens,
+                        const int* __restrict__ listed, const int* __restrict__ plan_head,
                         BiasedGeom g, int* status) {
   extern __shared__ float s_q[];                       // [BA_WARPS][head_dim]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int item = blockIdx.x * BA_WARPS + warp;       // (token, head) pairs, heads fastest
-  if (item >= n_tokens * g.n_heads) return;
-  const int t = item / g.n_heads, h = item - t * g.n_heads;
+  // with a list (the step's single-query tokens: flat index, request row, position per entry)
+  // only the listed tokens are served, as many as the list's head says
+  const int n_here = listed ? min(n_tokens, plan_head[0]) : n_tokens;
+  if (item >= n_here * g.n_heads) return;
+  const int entry = item / g.n_heads, h = item - entry * g.n_heads;
+  const int t = listed ? listed[3 * entry] : entry;
   const int r = tok_req[t];
   if (r < 0) return;
   const int D = g.head_dim;
@@ -238,12 +245,14 @@ HS_EXPORT int hs_biased_attention(void* out, const void* q, const void* pool, co
                                   int n_dist, const float* gate, int g_off, int g_stride,
                                   int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                                   int page_size, int num_pages, int max_pages, float scale,
-                                  float cap, int chunk, int window, int dtype, int* status,
+                                  float cap, int chunk, int window, int dtype,
+                                  const int* listed, const int* plan_head, int* status,
                                   void* stream) {
   if (!out || !q || !pool || !table || !tok_pos || !tok_req || !status) return HS_ERR_ARGUMENT;
   hs::BiasedGeom g = {n_heads, n_kv_heads, head_dim, page_size, num_pages, max_pages,
                       chunk, window, n_dist, scale, cap};
-  if (!biased_geom_ok(g) || (bias && n_dist <= 0) || cap < 0.f) return HS_ERR_UNSUPPORTED;
+  if (!biased_geom_ok(g) || (bias && n_dist <= 0) || cap < 0.f || (listed && !plan_head))
+    return HS_ERR_UNSUPPORTED;
   if (n_tokens <= 0) return HS_OK;
   cudaStream_t st = (cudaStream_t)stream;
   const long long items = (long long)n_tokens * n_heads;
@@ -252,11 +261,11 @@ HS_EXPORT int hs_biased_attention(void* out, const void* q, const void* pool, co
   if (dtype == HS_DT_F32)
     hs::biased_attention_kernel<float><<<blocks, hs::BA_WARPS * 32, smem, st>>>(
         (float*)out, (const float*)q, (const float*)pool, table, tok_pos, tok_req, bias, gate,
-        g_off, g_stride, n_tokens, g, status);
+        g_off, g_stride, n_tokens, listed, plan_head, g, status);
   else if (dtype == HS_DT_BF16)
     hs::biased_attention_kernel<__nv_bfloat16><<<blocks, hs::BA_WARPS * 32, smem, st>>>(
         (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)pool, table, tok_pos,
-        tok_req, bias, gate, g_off, g_stride, n_tokens, g, status);
+        tok_req, bias, gate, g_off, g_stride, n_tokens, listed, plan_head, g, status);
   else
     return HS_ERR_UNSUPPORTED;
   HS_LAUNCH_CHECK();

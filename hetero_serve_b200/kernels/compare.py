@@ -116,7 +116,34 @@ def _flops_and_bytes(name, args, kw, batch):
             return 7 * T * shape["heads"] * shape["dim"] * shape["vdim"], _nbytes(*args[2:7], o) + st
         if name == "delta_finish":
             return 0, _nbytes(args[0], args[1])
-        if name == "moe_route":
+        if name in ("rms_norm", "cast_rows"):
+            return 0, _nbytes(args[0]) + args[0].numel() * 4
+        if name == "rms_norm_add":
+            x, a = args[:2]
+            return 0, 2 * _nbytes(x) + _nbytes(a, kw.get("b"), kw.get("h"))
+        if name == "gated_act":
+            return 0, _nbytes(args[0], args[1])
+        if name == "qk_prepare":
+            q_out = args[0]
+            kv = q_out.shape[0] * kw["n_kv_heads"] * kw["head_dim"]
+            return 0, _nbytes(q_out) + q_out.numel() * 4 + kv * 4 + 2 * kv * q_out.element_size()
+        if name == "biased_attention":
+            out, q, pool = args[:3]
+            H, G, D, chunk = kw["n_heads"], kw["n_kv_heads"], kw["head_dim"], kw["chunk"]
+            seen = rows = 0
+            for start, n in batch:
+                for i in range(start, start + n):
+                    seen += (i % chunk if chunk else i) + 1
+                first = start // chunk * chunk if chunk else 0
+                rows += start + n - first               # distinct cache rows the portion reads
+            return 4 * H * D * seen, _nbytes(out, q) + rows * 2 * G * D * pool.element_size()
+        if name == "lightning_recurrence":
+            o, state, proj = args[:3]
+            H, D, V = kw["heads"], kw["dim"], kw["vdim"]
+            live = len([1 for _s, n in batch if n > 0])
+            cols = (2 * H * D + H * V) * 4
+            return 5 * o.shape[0] * H * D * V, _nbytes(o) + o.shape[0] * cols + 2 * live * H * D * V * 4
+        if name in ("moe_route", "moe_route_top"):
             h, wr = args[2], args[3]
             return 2 * h.shape[0] * wr.shape[0] * wr.shape[1], _nbytes(h, wr)
         if name == "moe_experts":

@@ -206,8 +206,10 @@ def _declare(lib) -> None:
         "hs_gated_act": [P, P, P, P, P, I, I, I, I, I, P],
         "hs_qk_prepare": [P, P, P, P, P, P, P, P, I, I, I, I, I, F, I, I, I, I, I, I, I, I, P, P],
         "hs_biased_attention": [P, P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, I, F, F, I, I,
-                                I, P, P],
-        "hs_lightning_recurrence": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P],
+                                I, P, P, P, P],
+        "hs_biased_attention_prefill": [P, P, P, P, P, P, I, P, P, I, P, I, I, I, I, I, I, I, I,
+                                        F, F, I, I, P, P],
+        "hs_lightning_recurrence": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, P],
         "hs_moe_sorted_scratch": [I, I, I, I, I, I, P, P],
         "hs_sample": [P, P, P, P, P, P, P, I, I, P, P, P, P],
     }
@@ -296,6 +298,9 @@ class CudaOps:
         self._skinny_need: dict = {}
         self._moe_need: dict = {}
         self.latent_mma = True      # prompt portions of latent attention on the tensor cores
+        self.biased_mma = True      # prompt portions of the biased chunk attention likewise
+        self.lightning_bulk_rows = 64   # from this many tokens a step on, lightning attention
+        #                                 activates its rows in a pass of their own
         self.latent_splits = None   # blocks a token's keys are split over in latent attention
         #                             (None: chosen from the number of tokens in the step)
         self.sorted_experts = True  # many (token, expert) pairs in bfloat16: sorted by expert and
@@ -1393,12 +1398,14 @@ class CudaOps:
 
     def biased_attention(self, out, q, pool, table, tok_pos, tok_req, *, bias, gate, gate_offset,
                          n_heads, n_kv_heads, head_dim, page_size, scale, cap, chunk, window,
-                         status):
+                         status, plan=None):
         """Causal softmax attention over the pages with score = cap * tanh(q . k * scale / cap)
         + bias[h, i - j] (``cap`` 0: none; ``bias`` float32 [heads, distances] or None), keys
         restricted to the query's chunk of ``chunk`` positions (0: none) and to the last
         ``window`` (0: all); head h's output is multiplied by sigmoid(gate[t, gate_offset + h])
-        when ``gate`` (float32 [T, *]) is given."""
+        when ``gate`` (float32 [T, *]) is given.  With the step's ``plan`` and a bfloat16 cache
+        the plan's tiles (prompt portions) run on the tensor cores and its single-query tokens
+        on the CUDA cores; without a plan every token runs on the CUDA cores."""
         _want(out, "out", _FLOATS, 2)
         _want(q, "q", out.dtype, 2)
         _want(pool, "pool", out.dtype)
@@ -1421,12 +1428,32 @@ class CudaOps:
         per_page = 2 * n_kv_heads * page_size * head_dim
         if pool.numel() % per_page:
             raise KernelError("biased_attention: the pool does not fit the sizes")
+        num_pages = pool.numel() // per_page
+        listed = head = None
+        if (plan is not None and plan.tile_cap > 0 and out.dtype == torch.bfloat16
+                and self.tensor_cores and self.biased_mma and plan.n_rows >= n):
+            d = plan.data
+            code = self.lib.hs_biased_attention_prefill(
+                _ptr(out), _ptr(q), _ptr(pool), _ptr(table),
+                _ptr(d[4 + plan_decode_ints(plan.n_rows):]), _ptr(d), plan.tile_cap,
+                _ptr(self._scratch_buffer("biased_counter", 1, torch.int32)), _ptr(bias), n_dist,
+                _ptr(gate), int(gate_offset), g_stride, n_heads, n_kv_heads, head_dim, page_size,
+                num_pages, table.shape[1], float(scale), float(cap), int(chunk), int(window),
+                _ptr(status), self._stream())
+            if code != -1:
+                _check(code, f"biased_attention_prefill(head_dim={head_dim})")
+                self.launches += 1
+                if plan.decode_cap == 0:
+                    return
+                listed, head = d[4:], d         # the CUDA-core kernel takes the single tokens
+                n = plan.decode_cap
         self.launches += 1
         _check(self.lib.hs_biased_attention(
             _ptr(out), _ptr(q), _ptr(pool), _ptr(table), _ptr(tok_pos), _ptr(tok_req), _ptr(bias),
             n_dist, _ptr(gate), int(gate_offset), g_stride, n, n_heads, n_kv_heads, head_dim,
-            page_size, pool.numel() // per_page, table.shape[1], float(scale), float(cap),
-            int(chunk), int(window), _DT[out.dtype], _ptr(status), self._stream()),
+            page_size, num_pages, table.shape[1], float(scale), float(cap),
+            int(chunk), int(window), _DT[out.dtype], _ptr(listed), _ptr(head), _ptr(status),
+            self._stream()),
             f"biased_attention(head_dim={head_dim})")
 
     # -- linear attention with a decay per head ---------------------------------------------
@@ -1448,11 +1475,18 @@ class CudaOps:
             raise KernelError("lightning_recurrence: the columns exceed the projection's row")
         if act not in ("none", "silu"):
             raise KernelError(f"lightning_recurrence: activation {act!r} not taken")
-        self.launches += 1
+        # steps of many tokens: the activations in a pass of their own into compact rows, which
+        # the recurrence then streams 16 bytes at a time (the same bits either way)
+        T = o.shape[0]
+        scratch = None
+        if T >= self.lightning_bulk_rows and dim % 4 == 0 and vdim % 4 == 0:
+            scratch = self._scratch_buffer("lightning_rows", T * (2 * heads * dim + heads * vdim),
+                                           torch.float32)
+        self.launches += 2 if scratch is not None else 1
         _check(self.lib.hs_lightning_recurrence(
             _ptr(o), _ptr(state), _ptr(proj), _ptr(decay), _ptr(req_start), _ptr(req_len),
-            _ptr(req_slot), req_start.shape[0], proj.shape[1], int(q_off), int(k_off), int(v_off),
-            heads, dim, vdim, ACTIVATIONS[act], self._stream()),
+            _ptr(req_slot), req_start.shape[0], T, proj.shape[1], int(q_off), int(k_off),
+            int(v_off), heads, dim, vdim, ACTIVATIONS[act], _ptr(scratch), self._stream()),
             f"lightning_recurrence(dim={dim},vdim={vdim})")
 
     # -- sampling ---------------------------------------------------------------

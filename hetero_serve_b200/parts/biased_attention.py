@@ -116,7 +116,8 @@ class BiasedChunkAttention(Mixer):
                              bias=self.bias, gate=proj, gate_offset=offset + qw + kw,
                              n_heads=self.H, n_kv_heads=self.G, head_dim=self.D,
                              page_size=cache.page_size, scale=self.scale, cap=self.cap,
-                             chunk=self.chunk, window=self.window, status=ctx.status)
+                             chunk=self.chunk, window=self.window, status=ctx.status,
+                             plan=getattr(ctx, "plan", None))
         ops.linear(out, att, self.w_out, self.b_out, residual=out if accumulate else None)
 
     def forward(self, ctx, h, x, cache, fresh=False):

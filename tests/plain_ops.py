@@ -399,7 +399,7 @@ class PlainOps:
 
     def biased_attention(self, out, q, pool, table, tok_pos, tok_req, *, bias, gate, gate_offset,
                          n_heads, n_kv_heads, head_dim, page_size, scale, cap, chunk, window,
-                         status):
+                         status, plan=None):
         pv = pool.view(-1, 2, n_kv_heads, page_size, head_dim)
         group = n_heads // n_kv_heads
         for t in range(out.shape[0]):

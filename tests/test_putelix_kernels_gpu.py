@@ -237,6 +237,57 @@ def test_a_far_key_among_hundreds_and_the_bias(ops, plain, dtype, tol):
         close(got[600:], want[600:], tol)
 
 
+@pytest.mark.parametrize("H, G, D, chunk, window", [(4, 2, 16, 24, 0), (2, 1, 64, 96, 0),
+                                                    (3, 3, 32, 0, 0), (2, 2, 128, 200, 70),
+                                                    (6, 2, 64, 7, 0), (2, 1, 48, 0, 33)])
+def test_prompt_portions_on_the_tensor_cores(ops, plain, H, G, D, chunk, window):
+    """The step's work list: portions of 150 and 131 queries that start in the middle of a
+    context (and of a chunk) as tiles on the tensor cores, a request bringing three tokens and
+    one bringing one on the CUDA cores; all against the twin, which knows no lists."""
+    page = 16
+    starts, news = (37, 0, 90, 11), (150, 131, 3, 1)
+    pos = torch.cat([torch.arange(s + n) for s, n in zip(starts, news)]).to(I32)
+    req = torch.cat([torch.full((s + n,), r) for r, (s, n) in enumerate(zip(starts, news))]).to(I32)
+    n = pos.shape[0]
+    stride = H * D + G * D + H
+    proj = rnd(n, stride, seed=15, std=0.6)
+    wq, wk = rnd(H * D, seed=16) * 0.2 + 1.2, rnd(G * D, seed=17) * 0.2 + 1.2
+    bias = rnd(H, max(chunk, window) or 256, seed=18)
+    pages = Pages(4, 200, page, G, D, BF16, seed=D)
+    # every token is prepared (the context fills the pages); the step's own tokens are queries
+    kw = dict(q_off=0, k_off=H * D, v_off=None, eps=1e-5, writes=True, n_heads=H, n_kv_heads=G,
+              head_dim=D, page_size=page)
+    q_want, pool_want = torch.zeros(n, H * D, dtype=F64), pages.pool.double().clone()
+    plain.qk_prepare(q_want, pool_want, proj, wq, wk, pages.table, pos, req, status=None, **kw)
+    status = torch.zeros(1, dtype=I32, device=DEV)
+    q_all = torch.zeros(n, H * D, dtype=BF16, device=DEV)
+    pool_got = dev(pages.pool.clone())
+    ops.qk_prepare(q_all, pool_got, dev(proj), dev(wq), dev(wk), dev(pages.table), dev(pos),
+                   dev(req), status=status, **kw)
+    # the step: the last `new` tokens of every request, flat and in request order
+    sel = torch.cat([torch.nonzero(req == r).flatten()[-m:] for r, m in enumerate(news)])
+    T = sel.shape[0]
+    akw = dict(bias=bias, gate_offset=H * D + G * D, n_heads=H, n_kv_heads=G, head_dim=D,
+               page_size=page, scale=0.35, cap=9.0, chunk=chunk, window=window)
+    want = torch.zeros(T, H * D, dtype=F64)
+    plain.biased_attention(want, q_want[sel], pool_want, pages.table, pos[sel], req[sel],
+                           gate=proj[sel], status=None, **akw)
+    plan = ops.make_plan([(r, r, s, m) for r, (s, m) in enumerate(zip(starts, news))], T, page)
+    assert plan.tile_cap == 4 and plan.decode_cap == 4
+    got = torch.full((T, H * D), float("nan"), dtype=BF16, device=DEV)
+    ops.biased_attention(got, q_all[dev(sel)].contiguous(), pool_got, dev(pages.table),
+                         dev(pos[sel]), dev(req[sel]), gate=dev(proj[sel]), status=status,
+                         plan=plan, **dict(akw, bias=dev(bias)))
+    assert int(status.item()) == 0
+    close(got, want, 5e-2)
+    # and the same rows through the CUDA-core kernel alone
+    slow = torch.zeros(T, H * D, dtype=BF16, device=DEV)
+    ops.biased_attention(slow, q_all[dev(sel)].contiguous(), pool_got, dev(pages.table),
+                         dev(pos[sel]), dev(req[sel]), gate=dev(proj[sel]), status=status,
+                         **dict(akw, bias=dev(bias)))
+    close(got, slow.cpu().double(), 4e-2)
+
+
 def test_attention_rows_do_not_depend_on_the_batch(ops, plain):
     """The same token alone and among others, its pages elsewhere: the same bits."""
     H, G, D, page = 4, 2, 16, 16
@@ -298,6 +349,36 @@ def test_lightning_in_portions_and_slots(ops, plain, H, D, V):
         close(got[r], want[r], 3e-6 * max(1.0, scale))
     close(state[3], state_w[3], 3e-6 * max(1.0, state_w.abs().max().item()))
     assert torch.isnan(state[0]).all() and torch.isnan(state[2]).all()
+
+
+@pytest.mark.parametrize("H, D, V", [(2, 64, 64), (1, 128, 32), (3, 16, 24), (1, 200, 36)])
+def test_lightning_many_tokens_a_step(ops, plain, H, D, V):
+    """Steps of many tokens activate their rows in a pass of their own and stream them; the
+    bits are those of the few-token path.  Portions of 100 and 70 tokens, then 90 and 3."""
+    stride = 2 * H * D + H * V + 5
+    kw = dict(q_off=5, k_off=5 + H * D, v_off=5 + 2 * H * D, heads=H, dim=D, vdim=V, act="silu")
+    decay = torch.tensor([0.999, 0.8, 0.5][:H])
+    seqs = [rnd(190, stride, seed=70), rnd(73, stride, seed=71)]
+    outs, states = [], []
+    for bulk_from in (64, 10 ** 9):
+        ops.lightning_bulk_rows = bulk_from
+        state = torch.zeros(2, H * D * V, device=DEV)
+        got = [torch.zeros(190, H * V), torch.zeros(73, H * V)]
+        for (a0, a1), (b0, b1) in (((0, 100), (0, 70)), ((100, 190), (70, 73))):
+            proj = dev(torch.cat([seqs[0][a0:a1], seqs[1][b0:b1]]))
+            o = torch.zeros(proj.shape[0], H * V, device=DEV)
+            ops.lightning_recurrence(o, state, proj, dev(decay), dev(ints(0, a1 - a0)),
+                                     dev(ints(a1 - a0, b1 - b0)), dev(ints(1, 0)), **kw)
+            got[0][a0:a1], got[1][b0:b1] = o[:a1 - a0].cpu(), o[a1 - a0:].cpu()
+        outs.append(got)
+        states.append(state.cpu())
+    ops.lightning_bulk_rows = 64
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    assert torch.equal(states[0], states[1])
+    want = torch.zeros(190, H * V, dtype=F64)
+    plain.lightning_recurrence(want, torch.zeros(1, H * D * V, dtype=F64), seqs[0], decay, ints(0),
+                               ints(190), ints(0), **kw)
+    close(outs[0][0], want, 1e-5)
 
 
 def test_lightning_long_decoding_is_bit_equal_to_one_portion(ops):
