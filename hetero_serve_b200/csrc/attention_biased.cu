@@ -50,6 +50,8 @@ qk_prepare_kernel(T* __restrict__ q_out, T* __restrict__ pool, const float* __re
                   const int* __restrict__ tok_req, int stride, int q_off, int k_off, int v_off,
                   float eps, int writes, BiasedGeom g, int* status) {
   __shared__ float s_part[QKP_THREADS / 32];
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int r = tok_req[t];
   if (r < 0) return;
@@ -129,7 +131,10 @@ biased_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
                         const float* __restrict__ gate, int g_off, int g_stride, int n_tokens,
                         const int* __restrict__ listed, const int* __restrict__ plan_head,
                         BiasedGeom g, int* status) {
-  extern __shared__ float s_q[];                       // [BA_WARPS][head_dim]
+  extern __shared__ __align__(16) unsigned char ba_smem[];
+  float* s_q = (float*)ba_smem;                        // [BA_WARPS][head_dim]
+  pdl_trigger();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int item = blockIdx.x * BA_WARPS + warp;       // (token, head) pairs, heads fastest
   // with a list (the step's single-query tokens: flat index, request row, position per entry)
@@ -141,6 +146,10 @@ biased_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
   const int r = tok_req[t];
   if (r < 0) return;
   const int D = g.head_dim;
+  // the warp's 32 value rows of a step: staged by 16-byte cp.async copies (a lane fetches its own
+  // key's row) while the scores are formed, then read with lane e on entries e, e + 32, ...
+  T* s_v = (T*)(ba_smem + ((BA_WARPS * D * sizeof(float) + 15) & ~(size_t)15)) + (size_t)warp * 32 * D;
+  const bool bulk = (D * sizeof(T)) % 16 == 0;
   const int i = tok_pos[t];
   const int hk = h / (g.n_heads / g.n_kv_heads);
   float* qs = s_q + warp * D;
@@ -167,6 +176,21 @@ biased_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
         krow = pool + ((size_t)page * 2 * g.n_kv_heads + hk) * tile + (size_t)(j % g.page_size) * D;
       }
     }
+    __syncwarp();                                      // the step before has read its value rows
+    if (krow) {
+      const T* vrow = krow + (size_t)g.n_kv_heads * tile;                        // plane 1
+      T* dst = s_v + (size_t)lane * D;
+      if (bulk) {
+        for (int b16 = 0; b16 < (int)(D * sizeof(T)); b16 += 16)
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
+                           (uint32_t)__cvta_generic_to_shared((char*)dst + b16)),
+                       "l"((const char*)vrow + b16)
+                       : "memory");
+      } else {
+        for (int d = 0; d < D; ++d) dst[d] = vrow[d];
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
     float s = -INFINITY;
     if (krow) {
       s = ba_dot(qs, krow, D) * g.scale;
@@ -179,13 +203,14 @@ biased_attention_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
     l = l * corr + warp_sum(pj);
 #pragma unroll
     for (int c = 0; c < BA_MAX_D / 32; ++c) acc[c] *= corr;
-    const int n_here = min(32, i - j0 + 1);
-    for (int k = 0; k < n_here; ++k) {
+    const unsigned have = __ballot_sync(0xffffffffu, krow != nullptr);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncwarp();                                      // every lane's row has landed
+    const int n_keys = min(32, i - j0 + 1);
+    for (int k = 0; k < n_keys; ++k) {
       const float pk = __shfl_sync(0xffffffffu, pj, k);
-      const unsigned long long vp =
-          __shfl_sync(0xffffffffu, (unsigned long long)(uintptr_t)krow, k);
-      if (vp == 0) continue;
-      const T* vrow = (const T*)(uintptr_t)vp + (size_t)g.n_kv_heads * tile;   // plane 1
+      if (!((have >> k) & 1u)) continue;
+      const T* vrow = s_v + (size_t)k * D;
 #pragma unroll
       for (int c = 0; c < BA_MAX_D / 32; ++c) {
         const int d = lane + 32 * c;
@@ -226,18 +251,19 @@ HS_EXPORT int hs_qk_prepare(void* q_out, void* pool, const float* proj, const fl
   if (!biased_geom_ok(g) || q_off < 0 || k_off < 0) return HS_ERR_UNSUPPORTED;
   if (n_tokens <= 0) return HS_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  const bool pdl = hs_pdl_enabled();
+  cudaError_t e = cudaSuccess;
   if (dtype == HS_DT_F32)
-    hs::qk_prepare_kernel<float><<<n_tokens, hs::QKP_THREADS, 0, st>>>(
+    e = hs_launch(hs::qk_prepare_kernel<float>, dim3(n_tokens), dim3(hs::QKP_THREADS), 0, st, pdl,
         (float*)q_out, (float*)pool, proj, wq, wk, table, tok_pos, tok_req, stride, q_off, k_off,
         v_off, eps, writes, g, status);
   else if (dtype == HS_DT_BF16)
-    hs::qk_prepare_kernel<__nv_bfloat16><<<n_tokens, hs::QKP_THREADS, 0, st>>>(
-        (__nv_bfloat16*)q_out, (__nv_bfloat16*)pool, proj, wq, wk, table, tok_pos, tok_req,
+    e = hs_launch(hs::qk_prepare_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(hs::QKP_THREADS), 0,
+        st, pdl, (__nv_bfloat16*)q_out, (__nv_bfloat16*)pool, proj, wq, wk, table, tok_pos, tok_req,
         stride, q_off, k_off, v_off, eps, writes, g, status);
   else
     return HS_ERR_UNSUPPORTED;
-  HS_LAUNCH_CHECK();
-  return HS_OK;
+  return e == cudaSuccess ? HS_OK : (int)e;
 }
 
 HS_EXPORT int hs_biased_attention(void* out, const void* q, const void* pool, const int* table,
@@ -255,19 +281,30 @@ HS_EXPORT int hs_biased_attention(void* out, const void* q, const void* pool, co
     return HS_ERR_UNSUPPORTED;
   if (n_tokens <= 0) return HS_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  const bool pdl = hs_pdl_enabled();
+  cudaError_t e = cudaSuccess;
   const long long items = (long long)n_tokens * n_heads;
   const int blocks = (int)((items + hs::BA_WARPS - 1) / hs::BA_WARPS);
-  const size_t smem = (size_t)hs::BA_WARPS * head_dim * sizeof(float);
+  const size_t esz = dtype == HS_DT_F32 ? 4 : 2;
+  const size_t smem = (((size_t)hs::BA_WARPS * head_dim * sizeof(float) + 15) & ~(size_t)15) +
+                      (size_t)hs::BA_WARPS * 32 * head_dim * esz;
+  if (smem > 48 * 1024) {
+    cudaError_t ea = dtype == HS_DT_F32
+        ? cudaFuncSetAttribute(hs::biased_attention_kernel<float>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+        : cudaFuncSetAttribute(hs::biased_attention_kernel<__nv_bfloat16>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (ea != cudaSuccess) return (int)ea;
+  }
   if (dtype == HS_DT_F32)
-    hs::biased_attention_kernel<float><<<blocks, hs::BA_WARPS * 32, smem, st>>>(
-        (float*)out, (const float*)q, (const float*)pool, table, tok_pos, tok_req, bias, gate,
+    e = hs_launch(hs::biased_attention_kernel<float>, dim3(blocks), dim3(hs::BA_WARPS * 32), smem,
+        st, pdl, (float*)out, (const float*)q, (const float*)pool, table, tok_pos, tok_req, bias, gate,
         g_off, g_stride, n_tokens, listed, plan_head, g, status);
   else if (dtype == HS_DT_BF16)
-    hs::biased_attention_kernel<__nv_bfloat16><<<blocks, hs::BA_WARPS * 32, smem, st>>>(
-        (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)pool, table, tok_pos,
+    e = hs_launch(hs::biased_attention_kernel<__nv_bfloat16>, dim3(blocks),
+        dim3(hs::BA_WARPS * 32), smem, st, pdl, (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)pool, table, tok_pos,
         tok_req, bias, gate, g_off, g_stride, n_tokens, listed, plan_head, g, status);
   else
     return HS_ERR_UNSUPPORTED;
-  HS_LAUNCH_CHECK();
-  return HS_OK;
+  return e == cudaSuccess ? HS_OK : (int)e;
 }

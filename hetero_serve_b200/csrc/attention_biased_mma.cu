@@ -108,6 +108,8 @@ biased_prefill_kernel(const BiasedPrefillParams p) {
   float* sB = (float*)(sV + BP_STAGES * BP_BKV * CPR);   // [min(n_dist, BP_MAX_BIAS)]
 
   __shared__ int s_item;
+  pdl_trigger();
+  pdl_wait();
   const int n_items = p.plan_head[1] * p.n_heads;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -351,9 +353,8 @@ static int launch_biased_prefill(const BiasedPrefillParams& p, cudaStream_t st) 
   }
   cudaError_t e = cudaMemsetAsync(p.work_counter, 0, sizeof(int), st);
   if (e != cudaSuccess) return (int)e;
-  kern<<<ctas, BP_WARPS * 32, smem, st>>>(p);
-  HS_LAUNCH_CHECK();
-  return HS_OK;
+  e = hs_launch(kern, dim3(ctas), dim3(BP_WARPS * 32), (size_t)smem, st, hs_pdl_enabled(), p);
+  return e == cudaSuccess ? HS_OK : (int)e;
 }
 
 }  // namespace hs

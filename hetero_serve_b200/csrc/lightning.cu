@@ -19,6 +19,8 @@ namespace hs {
 
 constexpr int LA_THREADS = 128;
 constexpr int LA_ROWS = 16;          // state rows a thread keeps
+constexpr int LA_PART = LA_ROWS + 4; // floats between two parts' rows of a token in shared memory:
+                                     // the parts of a column read 16-byte pieces from distinct banks
 constexpr int LA_TOK = 16;           // tokens staged at a time (8 when dim is above 128)
 
 __device__ __forceinline__ float la_act(float z, int act) {
@@ -33,14 +35,37 @@ __device__ __forceinline__ void la_cp16(void* smem_dst, const void* src) {
 __global__ void lightning_act_kernel(float* __restrict__ dst, const float* __restrict__ proj,
                                      int n_tokens, int stride, int q_off, int k_off, int v_off,
                                      int hd, int hv, int act) {
+  pdl_trigger();
+  pdl_wait();
   const int row_len = 2 * hd + hv;
-  const long long total = (long long)n_tokens * row_len;
-  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total;
-       e += (long long)gridDim.x * blockDim.x) {
-    const int t = (int)(e / row_len), c = (int)(e - (long long)t * row_len);
-    const int src = c < hd ? q_off + c : (c < 2 * hd ? k_off + c - hd : v_off + c - 2 * hd);
-    dst[e] = la_act(proj[(size_t)t * stride + src], act);
+  for (int t = blockIdx.x; t < n_tokens; t += gridDim.x) {
+    const float* row = proj + (size_t)t * stride;
+    float* out = dst + (size_t)t * row_len;
+    for (int c = threadIdx.x; c < row_len; c += blockDim.x) {
+      const int src = c < hd ? q_off + c : (c < 2 * hd ? k_off + c - hd : v_off + c - 2 * hd);
+      out[c] = la_act(row[src], act);
+    }
   }
+}
+
+// One token on a thread's 16 state rows: s <- decay s + k v, and the thread's share of o = S^T q
+// as four partial sums folded pairwise (the same order wherever the token stands).
+__device__ __forceinline__ float la_token(float (&s)[LA_ROWS], const float* kp, const float* qp,
+                                          float vt, float dh) {
+  float part_sum[LA_ROWS / 4];
+#pragma unroll
+  for (int i4 = 0; i4 < LA_ROWS / 4; ++i4) {
+    const float4 k4 = *(const float4*)(kp + 4 * i4), q4 = *(const float4*)(qp + 4 * i4);
+    s[4 * i4 + 0] = fmaf(k4.x, vt, dh * s[4 * i4 + 0]);
+    s[4 * i4 + 1] = fmaf(k4.y, vt, dh * s[4 * i4 + 1]);
+    s[4 * i4 + 2] = fmaf(k4.z, vt, dh * s[4 * i4 + 2]);
+    s[4 * i4 + 3] = fmaf(k4.w, vt, dh * s[4 * i4 + 3]);
+    float a = s[4 * i4 + 0] * q4.x;
+    a = fmaf(s[4 * i4 + 1], q4.y, a);
+    a = fmaf(s[4 * i4 + 2], q4.z, a);
+    part_sum[i4] = fmaf(s[4 * i4 + 3], q4.w, a);
+  }
+  return (part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]);
 }
 
 // A portion of up to ntok tokens of request rows (from token `tok` on) into one buffer (q [ntok][Dp],
@@ -58,8 +83,9 @@ __device__ __forceinline__ void la_stage(float* s_q, const float* __restrict__ p
     for (int e = threadIdx.x; e < here * dq; e += LA_THREADS) {
       const int tt = e / dq, c = e - tt * dq;
       const float* row = proj + (size_t)(tok + tt) * stride + (size_t)h * D + 4 * c;
-      la_cp16(s_q + tt * Dp + 4 * c, row + q_off);
-      la_cp16(s_k + tt * Dp + 4 * c, row + k_off);
+      const int at = tt * Dp + (4 * c) / LA_ROWS * LA_PART + (4 * c) % LA_ROWS;
+      la_cp16(s_q + at, row + q_off);
+      la_cp16(s_k + at, row + k_off);
     }
     for (int e = threadIdx.x; e < here * cq; e += LA_THREADS) {
       const int tt = e / cq, c = e - tt * cq;
@@ -72,8 +98,9 @@ __device__ __forceinline__ void la_stage(float* s_q, const float* __restrict__ p
     for (int e = threadIdx.x; e < here * D; e += LA_THREADS) {
       const int tt = e / D, d = e - tt * D;
       const float* row = proj + (size_t)(tok + tt) * stride + (size_t)h * D;
-      s_q[tt * Dp + d] = la_act(row[q_off + d], act);
-      s_k[tt * Dp + d] = la_act(row[k_off + d], act);
+      const int at = tt * Dp + d / LA_ROWS * LA_PART + d % LA_ROWS;
+      s_q[at] = la_act(row[q_off + d], act);
+      s_k[at] = la_act(row[k_off + d], act);
     }
     for (int e = threadIdx.x; e < here * cols; e += LA_THREADS) {
       const int tt = e / cols, c = e - tt * cols;
@@ -84,14 +111,16 @@ __device__ __forceinline__ void la_stage(float* s_q, const float* __restrict__ p
   asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
-__global__ void __launch_bounds__(LA_THREADS)
+__global__ void __launch_bounds__(LA_THREADS, 1)
 lightning_kernel(float* __restrict__ o, float* __restrict__ state, const float* __restrict__ proj,
                  const float* __restrict__ decay, const int* __restrict__ req_start,
                  const int* __restrict__ req_len, const int* __restrict__ req_slot, int stride,
                  int q_off, int k_off, int v_off, int H, int D, int V, int P, int act, int ntok,
                  int bulk) {
   extern __shared__ __align__(16) float smem[];
-  const int Dp = P * LA_ROWS;                       // dim padded to whole parts
+  pdl_trigger();
+  pdl_wait();
+  const int Dp = P * LA_PART;                       // a token's q (or k) row: P parts, padded
   const int cols = LA_THREADS / P;                  // value columns of this block
   const int per_buf = ntok * (2 * Dp + cols);       // a buffer: q [ntok][Dp], k [ntok][Dp], v [ntok][cols]
   const int r = blockIdx.z, h = blockIdx.y;
@@ -111,8 +140,10 @@ lightning_kernel(float* __restrict__ o, float* __restrict__ state, const float* 
     const int d = part * LA_ROWS + i;
     s[i] = (col_ok && d < D) ? S[(size_t)d * V + v] : 0.f;
   }
-  for (int e = threadIdx.x; e < 2 * per_buf; e += LA_THREADS) smem[e] = 0.f;   // the padding stays zero
-  __syncthreads();
+  if (D != P * LA_ROWS || V % cols) {               // rows or columns past the sizes read as zero
+    for (int e = threadIdx.x; e < 2 * per_buf; e += LA_THREADS) smem[e] = 0.f;
+    __syncthreads();
+  }
   la_stage(smem, proj, t0, min(ntok, n), stride, q_off, k_off, v_off, h, D, V, Dp, cols, v0, ntok,
            act, bulk);
   int buf = 0;
@@ -129,19 +160,26 @@ lightning_kernel(float* __restrict__ o, float* __restrict__ state, const float* 
     const float* s_q = smem + buf * per_buf;
     const float* s_k = s_q + ntok * Dp;
     const float* s_v = s_k + ntok * Dp;
-    for (int tt = 0; tt < here; ++tt) {
-      const float vt = s_v[tt * cols + col];
-      const float4* kq = (const float4*)(s_k + tt * Dp + part * LA_ROWS);
-      const float4* qq = (const float4*)(s_q + tt * Dp + part * LA_ROWS);
-      float acc = 0.f;
+    int tt = 0;
+    for (; tt + 4 <= here; tt += 4) {               // four tokens: their sums and folds overlap
+      float acc[4];
 #pragma unroll
-      for (int i4 = 0; i4 < LA_ROWS / 4; ++i4) {
-        const float4 k4 = kq[i4], q4 = qq[i4];
-        s[4 * i4 + 0] = fmaf(k4.x, vt, dh * s[4 * i4 + 0]); acc = fmaf(s[4 * i4 + 0], q4.x, acc);
-        s[4 * i4 + 1] = fmaf(k4.y, vt, dh * s[4 * i4 + 1]); acc = fmaf(s[4 * i4 + 1], q4.y, acc);
-        s[4 * i4 + 2] = fmaf(k4.z, vt, dh * s[4 * i4 + 2]); acc = fmaf(s[4 * i4 + 2], q4.z, acc);
-        s[4 * i4 + 3] = fmaf(k4.w, vt, dh * s[4 * i4 + 3]); acc = fmaf(s[4 * i4 + 3], q4.w, acc);
+      for (int u = 0; u < 4; ++u)
+        acc[u] = la_token(s, s_k + (tt + u) * Dp + part * LA_PART,
+                          s_q + (tt + u) * Dp + part * LA_PART, s_v[(tt + u) * cols + col], dh);
+      for (int off = 1; off < P; off <<= 1) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], off);
       }
+      if (part == 0 && col_ok) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          o[(size_t)(t0 + base + tt + u) * H * V + (size_t)h * V + v] = acc[u];
+      }
+    }
+    for (; tt < here; ++tt) {
+      float acc = la_token(s, s_k + tt * Dp + part * LA_PART, s_q + tt * Dp + part * LA_PART,
+                           s_v[tt * cols + col], dh);
       for (int off = 1; off < P; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
       if (part == 0 && col_ok) o[(size_t)(t0 + base + tt) * H * V + (size_t)h * V + v] = acc;
     }
@@ -175,27 +213,26 @@ HS_EXPORT int hs_lightning_recurrence(float* o, float* state, const float* proj,
   int P = 1;
   while (P * hs::LA_ROWS < D) P *= 2;
   const int cols = hs::LA_THREADS / P;
-  const int ntok = P * hs::LA_ROWS > 128 ? hs::LA_TOK / 2 : hs::LA_TOK;
+  const int ntok = P * hs::LA_ROWS > 128 ? hs::LA_TOK / 2 : hs::LA_TOK;   // at most 45 KB
   int bulk = 0;
   if (scratch && D % 4 == 0 && V % 4 == 0 && (((uintptr_t)scratch) & 15) == 0) {
     const int hd = H * D, hv = H * V;
-    const long long total = (long long)n_tokens * (2 * hd + hv);
-    long long blocks = (total + 255) / 256;
-    if (blocks > 148 * 16) blocks = 148 * 16;
-    hs::lightning_act_kernel<<<(int)blocks, 256, 0, st>>>(scratch, proj, n_tokens, stride, q_off,
-                                                         k_off, v_off, hd, hv, act);
-    HS_LAUNCH_CHECK();
+    int blocks = n_tokens < 148 * 8 ? n_tokens : 148 * 8;
+    cudaError_t e = hs_launch(hs::lightning_act_kernel, dim3(blocks), dim3(256), 0, st,
+                              hs_pdl_enabled(), scratch, proj, n_tokens, stride, q_off, k_off,
+                              v_off, hd, hv, act);
+    if (e != cudaSuccess) return (int)e;
     proj = scratch;
     stride = 2 * hd + hv;
     q_off = 0; k_off = hd; v_off = 2 * hd;
     act = HS_ACT_NONE;
     bulk = 1;
   }
-  const size_t smem = (size_t)2 * ntok * (2 * P * hs::LA_ROWS + cols) * sizeof(float);
+  const size_t smem = (size_t)2 * ntok * (2 * P * hs::LA_PART + cols) * sizeof(float);
   dim3 grid((V + cols - 1) / cols, H, n_requests);
-  hs::lightning_kernel<<<grid, hs::LA_THREADS, smem, st>>>(
-      o, state, proj, decay, req_start, req_len, req_slot, stride, q_off, k_off, v_off, H, D, V,
-      P, act, ntok, bulk);
-  HS_LAUNCH_CHECK();
+  cudaError_t e = hs_launch(hs::lightning_kernel, grid, dim3(hs::LA_THREADS), smem, st,
+                            hs_pdl_enabled(), o, state, proj, decay, req_start, req_len, req_slot,
+                            stride, q_off, k_off, v_off, H, D, V, P, act, ntok, bulk);
+  if (e != cudaSuccess) return (int)e;
   return HS_OK;
 }

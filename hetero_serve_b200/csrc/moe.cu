@@ -143,7 +143,7 @@ moe_route_kernel(int* __restrict__ sel_idx, float* __restrict__ sel_w, const TH*
 
 // One block per token: z = W_r h + b (or handed in), the `top` largest, softmax over the chosen.
 template <typename TH>
-__global__ void __launch_bounds__(ROUTE_THREADS)
+__global__ void __launch_bounds__(1024)
 moe_route_top_kernel(int* __restrict__ sel_idx, float* __restrict__ sel_w,
                      const TH* __restrict__ h, const float* __restrict__ w_router,
                      const float* __restrict__ bias, const int* __restrict__ tok_req, int width,
@@ -151,16 +151,18 @@ moe_route_top_kernel(int* __restrict__ sel_idx, float* __restrict__ sel_w,
   extern __shared__ float smem[];
   float* s_h = smem;                // [width]
   float* s_z = smem + width;        // [E] logits (-inf once taken)
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   if (tok_req[t] < 0) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (z_in) {
-    for (int e = threadIdx.x; e < E; e += ROUTE_THREADS)
+    for (int e = threadIdx.x; e < E; e += blockDim.x)
       s_z[e] = z_in[(size_t)t * E + e] + (bias ? bias[e] : 0.f);
   } else {
-    for (int k = threadIdx.x; k < width; k += ROUTE_THREADS) s_h[k] = to_f(h[(size_t)t * width + k]);
+    for (int k = threadIdx.x; k < width; k += blockDim.x) s_h[k] = to_f(h[(size_t)t * width + k]);
     __syncthreads();
-    for (int e = warp; e < E; e += ROUTE_THREADS / 32) {
+    for (int e = warp; e < E; e += blockDim.x / 32) {
       const float z = row_dot(w_router + (size_t)e * width, s_h, width, lane);
       if (lane == 0) s_z[e] = z + (bias ? bias[e] : 0.f);
     }
@@ -564,16 +566,19 @@ HS_EXPORT int hs_moe_route_top(int* sel_idx, float* sel_w, const void* h, const 
   const size_t smem = (size_t)(width + E) * sizeof(float);
   if (smem > 48 * 1024) return HS_ERR_UNSUPPORTED;
   cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e = cudaSuccess;
+  int threads = 32 * E;
+  threads = threads < 128 ? 128 : (threads > 1024 ? 1024 : threads);
   if (h_dtype == HS_DT_F32)
-    hs::moe_route_top_kernel<float><<<n_tokens, hs::ROUTE_THREADS, smem, st>>>(
-        sel_idx, sel_w, (const float*)h, w_router, bias, tok_req, width, E, top, z_in);
+    e = hs_launch(hs::moe_route_top_kernel<float>, dim3(n_tokens), dim3(threads), smem,
+                  st, hs_pdl_enabled(), sel_idx, sel_w, (const float*)h, w_router, bias, tok_req,
+                  width, E, top, z_in);
   else if (h_dtype == HS_DT_BF16)
-    hs::moe_route_top_kernel<__nv_bfloat16><<<n_tokens, hs::ROUTE_THREADS, smem, st>>>(
-        sel_idx, sel_w, (const __nv_bfloat16*)h, w_router, bias, tok_req, width, E, top, z_in);
+    e = hs_launch(hs::moe_route_top_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), smem, st, hs_pdl_enabled(), sel_idx, sel_w,
+                  (const __nv_bfloat16*)h, w_router, bias, tok_req, width, E, top, z_in);
   else
     return HS_ERR_UNSUPPORTED;
-  HS_LAUNCH_CHECK();
-  return HS_OK;
+  return e == cudaSuccess ? HS_OK : (int)e;
 }
 
 // Scratch of the sorted path for n_tokens x top pairs: ints (work lists, pair positions, row

@@ -58,6 +58,8 @@ gated_act_kernel(T* __restrict__ out, const T* __restrict__ gu, const T* __restr
                  const T* __restrict__ w_s, const int* __restrict__ tok_req, int ff, int width,
                  int act) {
   __shared__ float s_part[8];
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   if (tok_req && tok_req[t] < 0) return;
   float scale = 1.0f;
@@ -86,17 +88,18 @@ HS_EXPORT int hs_gated_act(void* out, const void* gu, const void* h, const void*
   if (ff <= 0 || act < HS_ACT_NONE || act > HS_ACT_LAST) return HS_ERR_UNSUPPORTED;
   if (n_tokens <= 0) return HS_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e = cudaSuccess;
   if (dtype == HS_DT_F32)
-    hs::gated_act_kernel<float><<<n_tokens, 256, 0, st>>>(
-        (float*)out, (const float*)gu, (const float*)h, (const float*)w_s, tok_req, ff, width, act);
+    e = hs_launch(hs::gated_act_kernel<float>, dim3(n_tokens), dim3(256), 0, st, hs_pdl_enabled(),
+                  (float*)out, (const float*)gu, (const float*)h, (const float*)w_s, tok_req, ff,
+                  width, act);
   else if (dtype == HS_DT_BF16)
-    hs::gated_act_kernel<__nv_bfloat16><<<n_tokens, 256, 0, st>>>(
-        (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, (const __nv_bfloat16*)h,
-        (const __nv_bfloat16*)w_s, tok_req, ff, width, act);
+    e = hs_launch(hs::gated_act_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), 0, st,
+                  hs_pdl_enabled(), (__nv_bfloat16*)out, (const __nv_bfloat16*)gu,
+                  (const __nv_bfloat16*)h, (const __nv_bfloat16*)w_s, tok_req, ff, width, act);
   else
     return HS_ERR_UNSUPPORTED;
-  HS_LAUNCH_CHECK();
-  return HS_OK;
+  return e == cudaSuccess ? HS_OK : (int)e;
 }
 
 HS_EXPORT int hs_dyt_norm(void* out, const float* x, const float* w, const float* b,

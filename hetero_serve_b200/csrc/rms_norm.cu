@@ -38,6 +38,8 @@ rms_norm_kernel(TO* __restrict__ out, const float* __restrict__ x, const float* 
                 const int* __restrict__ rows, int width, float eps, int one_plus,
                 const float* __restrict__ gate, int g_off, int g_stride) {
   __shared__ float s_part[RMS_THREADS / 32];
+  pdl_trigger();
+  pdl_wait();
   const int o = blockIdx.x;
   const int src = rows ? rows[o] : o;
   const float* xr = x + (size_t)src * width;
@@ -61,6 +63,8 @@ rms_norm_add_kernel(float* __restrict__ x, TH* __restrict__ h, const float* __re
                     int width, float eps_in, float eps) {
   extern __shared__ float s_y[];                       // [width]
   __shared__ float s_part[RMS_THREADS / 32];
+  pdl_trigger();
+  pdl_wait();
   const size_t row = (size_t)blockIdx.x * width;
   const float* ar = a + row;
   if (b) {
@@ -93,6 +97,8 @@ rms_norm_add_kernel(float* __restrict__ x, TH* __restrict__ h, const float* __re
 
 __global__ void cast_rows_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ x,
                                  long long n) {
+  pdl_trigger();
+  pdl_wait();
   long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
   const long long step = (long long)gridDim.x * blockDim.x * 4;
   for (; i < n; i += step) {
@@ -118,16 +124,18 @@ HS_EXPORT int hs_rms_norm(void* out, const float* x, const float* w, const int* 
   if (width <= 0) return HS_ERR_UNSUPPORTED;
   if (n_rows <= 0) return HS_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  const bool pdl = hs_pdl_enabled();
+  cudaError_t e = cudaSuccess;
   if (out_dtype == HS_DT_F32)
-    hs::rms_norm_kernel<float><<<n_rows, hs::RMS_THREADS, 0, st>>>(
-        (float*)out, x, w, rows, width, eps, one_plus, gate, g_off, g_stride);
+    e = hs_launch(hs::rms_norm_kernel<float>, dim3(n_rows), dim3(hs::RMS_THREADS), 0, st, pdl,
+                  (float*)out, x, w, rows, width, eps, one_plus, gate, g_off, g_stride);
   else if (out_dtype == HS_DT_BF16)
-    hs::rms_norm_kernel<__nv_bfloat16><<<n_rows, hs::RMS_THREADS, 0, st>>>(
-        (__nv_bfloat16*)out, x, w, rows, width, eps, one_plus, gate, g_off, g_stride);
+    e = hs_launch(hs::rms_norm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(hs::RMS_THREADS), 0, st,
+                  pdl, (__nv_bfloat16*)out, x, w, rows, width, eps, one_plus, gate, g_off,
+                  g_stride);
   else
     return HS_ERR_UNSUPPORTED;
-  HS_LAUNCH_CHECK();
-  return HS_OK;
+  return e == cudaSuccess ? HS_OK : (int)e;
 }
 
 // h_dtype: the type of the optional copy `h` (ignored when h is null).
@@ -140,23 +148,23 @@ HS_EXPORT int hs_rms_norm_add(float* x, void* h, const float* a, const float* wa
   const size_t smem = (size_t)width * sizeof(float);
   if (smem > 200 * 1024) return HS_ERR_UNSUPPORTED;
   cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e = cudaSuccess;
   if (h && h_dtype == HS_DT_BF16) {
     auto k = hs::rms_norm_add_kernel<__nv_bfloat16>;
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    k<<<n_rows, hs::RMS_THREADS, smem, st>>>(x, (__nv_bfloat16*)h, a, wa, b, wb, mix, w, width,
-                                             eps_in, eps);
+    e = hs_launch(k, dim3(n_rows), dim3(hs::RMS_THREADS), smem, st, hs_pdl_enabled(), x,
+                  (__nv_bfloat16*)h, a, wa, b, wb, mix, w, width, eps_in, eps);
   } else if (!h || h_dtype == HS_DT_F32) {
     auto k = hs::rms_norm_add_kernel<float>;
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    k<<<n_rows, hs::RMS_THREADS, smem, st>>>(x, (float*)h, a, wa, b, wb, mix, w, width,
-                                             eps_in, eps);
+    e = hs_launch(k, dim3(n_rows), dim3(hs::RMS_THREADS), smem, st, hs_pdl_enabled(), x,
+                  (float*)h, a, wa, b, wb, mix, w, width, eps_in, eps);
   } else {
     return HS_ERR_UNSUPPORTED;
   }
-  HS_LAUNCH_CHECK();
-  return HS_OK;
+  return e == cudaSuccess ? HS_OK : (int)e;
 }
 
 HS_EXPORT int hs_cast_rows(void* out, const float* x, long long n, void* stream) {
@@ -165,7 +173,7 @@ HS_EXPORT int hs_cast_rows(void* out, const float* x, long long n, void* stream)
   long long blocks = (n / 4 + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   if (blocks < 1) blocks = 1;
-  hs::cast_rows_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)out, x, n);
-  HS_LAUNCH_CHECK();
-  return HS_OK;
+  cudaError_t e = hs_launch(hs::cast_rows_kernel, dim3((int)blocks), dim3(256), 0,
+                            (cudaStream_t)stream, hs_pdl_enabled(), (__nv_bfloat16*)out, x, n);
+  return e == cudaSuccess ? HS_OK : (int)e;
 }
