@@ -63,9 +63,12 @@ def chain_hashes(token_ids: Sequence[int], page_size: int) -> list[int]:
 
 @dataclass(frozen=True)
 class GroupSpec:
-    """One page group: ``window == 0`` keeps every position, ``window == w`` the last w."""
+    """One page group: ``window == 0`` keeps every position, ``window == w`` the last w;
+    ``chunk == c`` keeps the positions of the chunk of c the request's next token falls in
+    (chunks counted from position 0)."""
 
     window: int = 0
+    chunk: int = 0
     num_pages: int | None = None      # None → the manager's default
 
 
@@ -213,7 +216,7 @@ class CacheManager:
         # a shared prefix is only sound when every group still holds it and no mixer keeps
         # state beside the pages
         self.prefix_cache = (prefix_cache and not has_state and len(self.groups) > 0
-                             and all(g.window == 0 for g in self.groups))
+                             and all(g.window == 0 and g.chunk == 0 for g in self.groups))
         self.pools = [PagePool(g.num_pages or num_pages, self.prefix_cache) for g in self.groups]
         self.max_requests = max_requests
         self._free_slots = list(range(max_requests - 1, -1, -1))
@@ -361,8 +364,8 @@ class CacheManager:
                     pool.drop(page)
 
     def commit(self, req_id, new_len: int) -> None:
-        """Positions < new_len are now resident.  Pages of a windowed group that no later
-        query can reach are given back at once."""
+        """Positions < new_len are now resident.  Pages of a windowed or chunked group that no
+        later query can reach are given back at once."""
         req = self._get(req_id)
         if new_len < req.length:
             raise CacheError("a request's length cannot shrink")
@@ -370,10 +373,15 @@ class CacheManager:
             raise CacheError("commit beyond the reserved pages")
         req.length = new_len
         for gi, g in enumerate(self.groups):
-            if g.window <= 0:
+            if g.window <= 0 and g.chunk <= 0:
                 continue
-            # the next query sits at position >= new_len and reads keys > new_len - window
-            first_needed = max(0, new_len - g.window + 1)
+            first_needed = 0
+            if g.window > 0:
+                # the next query sits at position >= new_len and reads keys > new_len - window
+                first_needed = max(0, new_len - g.window + 1)
+            if g.chunk > 0:
+                # ... and no key before the start of the chunk that position new_len lies in
+                first_needed = max(first_needed, new_len // g.chunk * g.chunk)
             keep_from = first_needed // self.page_size
             table = req.tables[gi]
             for i in range(req.first_live[gi], min(keep_from, len(table))):
@@ -429,7 +437,7 @@ class CacheManager:
                "hits": self.hit_tokens, "misses": self.miss_tokens, "groups": []}
         for g, pool in zip(self.groups, self.pools):
             out["groups"].append({
-                "window": g.window, "num_blocks": pool.num_pages, "used": pool.num_used,
+                "window": g.window, "chunk": g.chunk, "num_blocks": pool.num_pages, "used": pool.num_used,
                 "free": pool.num_free, "cached_blocks": len(pool._hash_to_page),
                 "evictable": len(pool._evictable), "evictions": pool.evictions,
                 "utilisation": round(pool.num_used / pool.num_pages, 4)})

@@ -246,7 +246,7 @@ class Runner:
         if model.dtype != dtype:
             raise StepError("the model was bound with another dtype than the runner's")
         self.manager = CacheManager(
-            [GroupSpec(window=g.window) for g in model.cache_groups], num_pages, page_size,
+            [GroupSpec(window=g.window, chunk=getattr(g, "chunk", 0)) for g in model.cache_groups], num_pages, page_size,
             max_requests, prefix_cache=prefix_cache, has_state=bool(model.state_shapes))
         self.storage = CacheStorage(model, self.manager, dtype, self.device)
         self.manager.on_open = self._clear_slot

@@ -48,12 +48,15 @@ class TensorRequest:
 class CacheRequest:
     """What a mixer wants kept per token: ``planes`` rows of ``kv_heads x head_dim`` (two,
     keys and values, for ordinary attention; one for a mixer that keeps a single shared
-    vector per token), all of them (``window == 0``) or the last ``window`` positions."""
+    vector per token), all of them (``window == 0``) or the last ``window`` positions.  With
+    ``chunk`` a query reads only keys of its own chunk of that many positions (chunks counted
+    from position 0): the rows of chunks that have passed are never read again."""
 
     kv_heads: int
     head_dim: int
     window: int = 0
     planes: int = 2
+    chunk: int = 0
 
 
 class Part:

@@ -17,7 +17,8 @@ ln(bias_max / (B/2)) * (B - B/2))).  The rows are expanded once at binding into 
 positions.
 
 The cache keeps two planes per token and key/value head: the normed keys and the values (the
-un-normed keys), so the attention kernel reads what any attention kernel reads.  q, k and the
+un-normed keys), so the attention kernel reads what any attention kernel reads; the cache
+manager gives the pages of chunks that have passed back at once.  q, k and the
 gate's logits are ONE product; norms, scores, softmax and the gate are float32 in both
 precisions.  The mixer can also run on a slice of a wider projection that a mixer around it
 formed (``input_projection`` / ``forward_projected``).
@@ -96,7 +97,7 @@ class BiasedChunkAttention(Mixer):
         self.w_out, self.b_out = t[p + "o"], t[p + "o.b"]
 
     def cache_request(self):
-        return CacheRequest(self.G, self.D, self.window)
+        return CacheRequest(self.G, self.D, self.window, 2, self.chunk)
 
     def input_projection(self):
         """(weight [n, width], bias [n]) of this mixer's columns in a projection of the input;

@@ -159,6 +159,7 @@ class CacheGroup:
     window: int
     entries: tuple[int, ...]        # cache entry numbers, in pool order
     planes: int = 2                 # rows kept per token and head (keys and values: two)
+    chunk: int = 0                  # > 0: only the rows of the chunk the request is in are kept
 
 
 class Model:
@@ -219,7 +220,7 @@ class Model:
         for entry in sorted(entry_req):
             groups.setdefault(entry_req[entry], []).append(entry)
         self.cache_groups: list[CacheGroup] = [
-            CacheGroup(r.kv_heads, r.head_dim, r.window, tuple(es), r.planes)
+            CacheGroup(r.kv_heads, r.head_dim, r.window, tuple(es), r.planes, r.chunk)
             for r, es in groups.items()]
         self.entry_location: dict[int, tuple[int, int]] = {}
         for gi, g in enumerate(self.cache_groups):

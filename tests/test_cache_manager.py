@@ -113,6 +113,31 @@ def test_windowed_group_gives_pages_back_as_the_window_passes():
     m.check()
 
 
+def test_chunked_group_gives_pages_back_as_chunks_pass():
+    """A query reads only keys of its own chunk: once the next token falls into a new chunk the
+    pages that lie wholly before that chunk's start are back, at any cut of the request."""
+    m = CacheManager([GroupSpec(), GroupSpec(chunk=40), GroupSpec(chunk=100, window=30)],
+                     num_pages=16, page_size=16, max_requests=2)
+    assert not m.prefix_cache                           # chunks rule prefix reuse out
+    m.open("a")
+    m.reserve("a", 79); m.commit("a", 79)
+    # the next token (position 79) lies in chunk [40, 80): page 0..1 hold positions < 32
+    assert m.table("a", 1)[:2] == [-1, -1] and all(p >= 0 for p in m.table("a", 1)[2:])
+    assert all(p >= 0 for p in m.table("a", 0))
+    m.reserve("a", 80); m.commit("a", 80)
+    # position 80 opens chunk [80, 120): everything before page 5 (position 80) is back
+    assert m.table("a", 1) == [-1] * 5
+    assert m.pages_free(1) == 16 and m.pages_free(0) == 16 - 5
+    m.reserve("a", 130); m.commit("a", 130)
+    # chunk of 100 with a window of 30: position 130 reads keys >= max(100, 101)
+    assert m.table("a", 2)[:6] == [-1] * 6 and all(p >= 0 for p in m.table("a", 2)[6:])
+    assert m.table("a", 1)[:7] == [-1] * 7               # chunk [120, 160): pages before 112
+    m.check()
+    m.close("a")
+    assert all(m.pages_free(g) == 16 for g in range(3))
+    m.check()
+
+
 def test_state_slots():
     m = CacheManager([GroupSpec()], num_pages=4, page_size=16, max_requests=2)
     a, b = m.open("a").slot, m.open("b").slot

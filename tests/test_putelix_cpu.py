@@ -72,6 +72,7 @@ def test_spec_has_one_page_group_and_a_state_per_layer(putelix_cases):
     model = Model(arch.build_spec(arch.config_cls.from_dict(case.config)))
     groups = {(g.kv_heads, g.head_dim, g.planes): len(g.entries) for g in model.cache_groups}
     assert groups == {(2, 16, 2): 2, (3, 8, 2): 1}          # normed keys and values, two planes
+    assert sorted(g.chunk for g in model.cache_groups) == [24, 37]
     assert model.state_shapes == {0: (3 * 8 * 12,), 1: (2 * 16 * 8,), 2: (3 * 8 * 12,)}
     assert model.blocks[2].feed_forward is None and model.blocks[2].norm2 is None
     assert model.spec.max_positions == 300
@@ -188,6 +189,26 @@ def test_a_slot_is_cleared_for_its_next_owner(putelix_cases):
     res = rn.step([StepEntry("b", b[10:], want=[6])])
     assert (res.logits[0].double() - case.logits(b)[16]).abs().max() < TOL
     rn.manager.check()
+
+
+def test_pages_of_passed_chunks_are_given_back(putelix_cases):
+    """A request far longer than the pool holds runs in portions, because the pages of the
+    chunks behind it are given back as it goes; its logits are the plain model's."""
+    case = putelix_cases["case_a"]                    # chunks of 24 and 37 positions, pages of 16
+    model, _ = load_model(case.dir, "float32", "cpu")
+    rn = Runner(model, num_pages=6, page_size=16, max_requests=1, dtype=torch.float32,
+                device="cpu", ops=plain_ops.PlainOps())
+    toks = case.tokens(230, 17)
+    want, at = case.logits(toks), 0
+    for n in (20, 13, 2, 19, 1, 1, 20, 7, 20, 20, 3, 20, 1, 20, 20, 20, 2, 20, 1):
+        res = rn.step([StepEntry("a", toks[at:at + n], want=[n - 1])])
+        assert (res.logits[0].double() - want[at + n - 1]).abs().max() < TOL, at
+        at += n
+        assert all(6 - rn.manager.pages_free(g) <= 5 for g in range(len(model.cache_groups)))
+    assert at == 230
+    rn.manager.check()
+    rn.close("a")
+    assert all(rn.manager.pages_free(g) == 6 for g in range(len(model.cache_groups)))
 
 
 def test_the_parts_under_an_arrangement_that_adds(putelix_cases):
