@@ -149,7 +149,10 @@ biased_prefill_kernel(const BiasedPrefillParams p) {
   for (int c = threadIdx.x; c < n_bias; c += blockDim.x) sB[c] = p.bias[(size_t)h * p.n_dist + c];
   const float* gbias = p.bias ? p.bias + (size_t)h * p.n_dist : nullptr;
 
-  const int kt_first = bp_first_key(pos0, p.chunk, p.window) / BP_BKV;
+  // keys before the first key the item's first query sees are never read: their pages may have
+  // been given back already (the rows of such a tile's head are filled with zeros)
+  const int key_lo = bp_first_key(pos0, p.chunk, p.window);
+  const int kt_first = key_lo / BP_BKV;
   const int kt_end = pos_last / BP_BKV + 1;
   auto load_tile = [&](int kt, int stage) {
     uint4* dK = sK + stage * BP_BKV * CPR;
@@ -158,7 +161,7 @@ biased_prefill_kernel(const BiasedPrefillParams p) {
       const int row = c / CPR, ch = c % CPR;
       const int j = kt * BP_BKV + row;
       const int dst = swz<D>(row, ch);
-      bool ok = j <= pos_last;
+      bool ok = j <= pos_last && j >= key_lo;
       int page = 0;
       int slot_in_page = 0;
       if (ok) {

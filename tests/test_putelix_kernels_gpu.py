@@ -275,7 +275,15 @@ def test_prompt_portions_on_the_tensor_cores(ops, plain, H, G, D, chunk, window)
     plan = ops.make_plan([(r, r, s, m) for r, (s, m) in enumerate(zip(starts, news))], T, page)
     assert plan.tile_cap == 4 and plan.decode_cap == 4
     got = torch.full((T, H * D), float("nan"), dtype=BF16, device=DEV)
-    ops.biased_attention(got, q_all[dev(sel)].contiguous(), pool_got, dev(pages.table),
+    # the pages that lie wholly before the first key a request's first query sees have been
+    # given back: the kernels must not look them up
+    freed = pages.table.clone()
+    for r, s0 in enumerate(starts):
+        lo = s0 // chunk * chunk if chunk else 0
+        if window:
+            lo = max(lo, s0 - window + 1)
+        freed[r, :lo // page] = -1
+    ops.biased_attention(got, q_all[dev(sel)].contiguous(), pool_got, dev(freed),
                          dev(pos[sel]), dev(req[sel]), gate=dev(proj[sel]), status=status,
                          plan=plan, **dict(akw, bias=dev(bias)))
     assert int(status.item()) == 0
