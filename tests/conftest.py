@@ -114,6 +114,6 @@ def putelix_cases(tmp_path_factory):
     return uc.make_cases(tmp_path_factory)
 
 
-@pytest.fixture(params=["case_a", "case_b"])
+@pytest.fixture(params=["case_a", "case_b", "case_d"])
 def putelix_case(request, putelix_cases):
     return putelix_cases[request.param]

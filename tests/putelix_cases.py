@@ -63,7 +63,17 @@ CASE_C = _model(512, 128, 640, 1e-6, [
            _moe(64, 8, 2, shared=96)),
 ])
 
-CASES = {"case_a": (CASE_A, 21), "case_b": (CASE_B, 22), "case_c": (CASE_C, 23)}
+# sizes no fast path takes: a head size that is no multiple of 16, five ungrouped heads, widths
+# and inner sizes that are no multiple of 32, seven experts of which three are chosen
+CASE_D = _model(301, 72, 400, 1e-6, [
+    _layer(_left(5, 5, 24, 100, 0.2, 12.0, 150, 20), _right(2, 40, 36, [0.93, 0.999]),
+           _moe(40, 7, 3, shared=24)),
+    _layer(_left(5, 1, 24, 100, 0.2, 12.0, 150, 20), _right(2, 40, 36, [0.93, 0.999]),
+           {"kind": "dense", "ff": 100}),
+])
+
+CASES = {"case_a": (CASE_A, 21), "case_b": (CASE_B, 22), "case_c": (CASE_C, 23),
+         "case_d": (CASE_D, 24)}
 
 
 class Case:

@@ -115,6 +115,20 @@ def test_linear_activations(ops, plain, act, dtype, M, tol):
     close(got2, want2, tol if dtype == F32 else 8e-2)
 
 
+@pytest.mark.parametrize("M", [3, 40, 300])
+@pytest.mark.parametrize("N", [5, 6, 518])
+def test_linear_with_few_or_odd_output_columns(ops, plain, M, N):
+    """Router logits (a handful of experts) and the mixer's fused projection (a width that is
+    no multiple of 4) as float32 outputs of bfloat16 products."""
+    a, w, bias = rnd(M, 64, seed=5).to(BF16), rnd(N, 64, seed=6, std=0.2).to(BF16), rnd(N, seed=7)
+    for b in (bias, None):
+        want = torch.zeros(M, N, dtype=F64)
+        plain.linear(want, a, w, b)
+        got = torch.full((M, N), float("nan"), dtype=F32, device=DEV)
+        ops.linear(got, dev(a), dev(w), None if b is None else dev(b))
+        close(got, want, 2e-5)
+
+
 # -- attention with a distance bias, a cap and chunks -------------------------------------------
 class Pages:
     """A request's pages scattered over a pool whose unused rows are NaN."""
