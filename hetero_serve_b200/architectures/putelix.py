@@ -78,6 +78,16 @@ def _check_mlp(i: int, mlp) -> None:
         positive_int(f"{where}.shared.ff", need(_section(mlp, "shared", where), "ff"))
 
 
+def _decays(right: Mapping, where: str) -> list:
+    """One decay per lightning head; a single number stands for all heads."""
+    decay = need(right, "decay")
+    if isinstance(decay, (int, float)) and not isinstance(decay, bool):
+        return [decay] * right["heads"]
+    if not isinstance(decay, (list, tuple)) or len(decay) != right["heads"]:
+        raise ConfigError(f"{where}.decay must list one decay per head")
+    return list(decay)
+
+
 def _check_layer(i: int, layer) -> None:
     where = f"layers[{i}]"
     if not isinstance(layer, Mapping) or layer.get("type") not in LAYER_TYPES:
@@ -97,10 +107,7 @@ def _check_layer(i: int, layer) -> None:
     positive_int(f"{wl}.mask.size", need(_section(left, "mask", wl), "size"))
     for key in ("heads", "dim", "vdim"):
         positive_int(f"{wr}.{key}", need(right, key))
-    decay = need(right, "decay")
-    if not isinstance(decay, (list, tuple)) or len(decay) != right["heads"]:
-        raise ConfigError(f"{wr}.decay must list one decay per head")
-    for d in decay:
+    for d in _decays(right, wr):
         _number(f"{wr}.decay[]", d)
     _check_mlp(i, layer.get("mlp"))
 
@@ -153,7 +160,7 @@ def build_spec(cfg: PutelixConfig) -> ModelSpec:
             prefix=p + "mix.left."))
         lightning = PartSpec("lightning_attention", dict(
             width=W, n_heads=right["heads"], dim=right["dim"], vdim=right["vdim"],
-            decay=tuple(right["decay"]), eps=eps, prefix=p + "mix.right."))
+            decay=tuple(_decays(right, p + "mixer.right")), eps=eps, prefix=p + "mix.right."))
         mixer = PartSpec("normed_pair", dict(
             width=W, eps=eps, left=attention, right=lightning, left_weight=p + "mix.left.out",
             right_weight=p + "mix.right.out", mix=0.5))
