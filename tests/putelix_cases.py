@@ -57,18 +57,18 @@ CASE_B = _model(257, 40, 200, 1e-6, [
 ])
 # sizes the tile kernels take (multiples of 32, heads of 64), stored in bfloat16
 CASE_C = _model(512, 128, 640, 1e-6, [
-    _layer(_left(4, 1, 32, 64, 0.18, 20.0, 48, 16), _right(2, 64, 32, [0.8, 0.995]),
+    _layer(_left(4, 1, 32, 64, 0.18, 25.0, 48, 16), _right(2, 64, 32, [0.8, 0.995]),
            {"kind": "dense", "ff": 256}),
-    _layer(_left(4, 1, 32, 64, 0.18, 20.0, 48, 16), _right(2, 64, 32, [0.8, 0.995]),
+    _layer(_left(4, 1, 32, 64, 0.18, 25.0, 48, 16), _right(2, 64, 32, [0.8, 0.995]),
            _moe(64, 8, 2, shared=96)),
 ])
 
 # sizes no fast path takes: a head size that is no multiple of 16, five ungrouped heads, widths
 # and inner sizes that are no multiple of 32, seven experts of which three are chosen
 CASE_D = _model(301, 72, 400, 1e-6, [
-    _layer(_left(5, 5, 24, 100, 0.2, 12.0, 150, 20), _right(2, 40, 36, [0.93, 0.999]),
+    _layer(_left(5, 5, 24, 100, 0.2, 12.0, 150, 20), _right(2, 40, 36, [0.93, 0.998]),
            _moe(40, 7, 3, shared=24)),
-    _layer(_left(5, 1, 24, 100, 0.2, 12.0, 150, 20), _right(2, 40, 36, [0.93, 0.999]),
+    _layer(_left(5, 1, 24, 100, 0.2, 12.0, 150, 20), _right(2, 40, 36, [0.93, 0.998]),
            {"kind": "dense", "ff": 100}),
 ])
 

@@ -118,13 +118,13 @@ def test_rows_of_the_distance_table_come_from_the_tensor(putelix_cases, tmp_path
 
 # -- the plain implementation's own sanity and the table the package expands ----------------
 def test_distance_buckets():
-    rows = [plain_putelix.distance_bucket(n, 32, 240) for n in range(400)]
-    assert rows[:16] == list(range(16)) and rows[16] == 16 and rows[239] == 31 and rows[399] == 31
+    rows = [plain_putelix.distance_bucket(n, 32, 200) for n in range(400)]
+    assert rows[:16] == list(range(16)) and rows[16] == 16 and rows[199] == 31 and rows[399] == 31
     assert all(b >= a for a, b in zip(rows, rows[1:]))
     first_31 = rows.index(31)
-    assert math.log(first_31 / 16) / math.log(240 / 16) * 16 >= 15 > \
-        math.log((first_31 - 1) / 16) / math.log(240 / 16) * 16
-    for B, far in ((32, 240), (10, 20), (6, 5), (14, 30), (2, 9)):
+    assert math.log(first_31 / 16) / math.log(200 / 16) * 16 >= 15 > \
+        math.log((first_31 - 1) / 16) / math.log(200 / 16) * 16
+    for B, far in ((32, 200), (10, 20), (6, 5), (14, 30), (2, 9)):
         assert distance_buckets(300, B, far) == [plain_putelix.distance_bucket(n, B, far)
                                                  for n in range(300)]
 
